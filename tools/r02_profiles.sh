@@ -4,7 +4,7 @@ set -x
 ncu --metrics gpu__time_duration.sum --clock-control none -c 14000 --csv --log-file gpurun_out/r02_launches.csv \
     python bench.py --steps 1 --warmup 1 --layers 4 --decode 16 --no-cpu-baseline --no-fixed-total > gpurun_out/r02_ncu_bench.log 2>&1
 tail -2 gpurun_out/r02_ncu_bench.log | cut -c1-300
-ncu --set full --clock-control none --import-source on -k regex:gemm_skinny --launch-skip 60 --launch-count 5 -f -o gpurun_out/r02_decode_gemm \
+ncu --set full --clock-control none -k regex:gemm_skinny --launch-skip 60 --launch-count 5 -f -o gpurun_out/r02_decode_gemm \
     python bench.py --steps 1 --warmup 1 --layers 2 --decode 8 --no-cpu-baseline --no-fixed-total > gpurun_out/r02_ncu_gemm.log 2>&1
 tail -2 gpurun_out/r02_ncu_gemm.log | cut -c1-300
 timeout 900 compute-sanitizer --tool memcheck --error-exitcode 1 python -m pytest tests/test_scheduler_gpu.py tests/test_features_gpu.py \
