@@ -15,7 +15,7 @@ class EngineCfg(C.Structure):
                 ("max_ctx", C.c_int32), ("max_batched_tokens", C.c_int32), ("kv_page_size", C.c_int32),
                 ("use_cuda_graphs", C.c_int32), ("enable_prefix_cache", C.c_int32), ("sm_budget", C.c_int32),
                 ("sm_partition", C.c_int32), ("stream_priority", C.c_int32), ("decode_with_prefill", C.c_int32),
-                ("fused_decode", C.c_int32), ("mixed_step_tokens", C.c_int32)]
+                ("fused_decode", C.c_int32), ("mixed_step_tokens", C.c_int32), ("kv_pool_tokens", C.c_int32)]
 
 
 class ModelDescC(C.Structure):
@@ -25,6 +25,22 @@ class ModelDescC(C.Structure):
                 ("norm_eps", C.c_float), ("rope_theta", C.c_float), ("rope_factor", C.c_float),
                 ("rope_low_freq_factor", C.c_float), ("rope_high_freq_factor", C.c_float),
                 ("rope_orig_max_pos", C.c_int32), ("qkv_bias", C.c_int32), ("reserved", C.c_int32 * 7)]
+
+
+class LayerDescC(C.Structure):
+    _fields_ = [("mixer", C.c_int32), ("heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("tau", C.c_float),
+                ("decay_rank", C.c_int32), ("q_rank", C.c_int32), ("kv_rank", C.c_int32), ("rot_dim", C.c_int32),
+                ("rope_dims", C.c_int32), ("window", C.c_int32), ("kv_from", C.c_int32), ("rope_base", C.c_float),
+                ("scale", C.c_float), ("ff", C.c_int32), ("ff_limit", C.c_float), ("reserved", C.c_int32 * 4)]
+
+
+class StackDescC(C.Structure):
+    _fields_ = [("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("compute_f32", C.c_int32),
+                ("norm_eps", C.c_float), ("resid_alpha", C.c_float), ("logit_softcap", C.c_float), ("reserved", C.c_int32 * 5)]
+
+
+class SeqFeedC(C.Structure):
+    _fields_ = [("seq", C.c_uint64), ("tokens", C.c_void_p), ("n_tokens", C.c_int32), ("want", C.c_void_p), ("n_want", C.c_int32)]
 
 
 class SamplingC(C.Structure):
@@ -62,6 +78,11 @@ SIGNATURES = {
     "hb_model_tensor_set": (I, [P, C.c_char_p, P, C.c_size_t]),
     "hb_model_load_finish": (I, [P]),
     "hb_model_load_random": (I, [P, C.POINTER(ModelDescC), C.c_uint64]),
+    "hb_model_load_begin_stack": (I, [P, C.POINTER(StackDescC), C.POINTER(LayerDescC)]),
+    "hb_model_load_random_stack": (I, [P, C.POINTER(StackDescC), C.POINTER(LayerDescC), C.c_uint64]),
+    "hb_seq_open": (I, [P, C.POINTER(C.c_uint64)]),
+    "hb_seq_step": (I, [P, C.POINTER(SeqFeedC), C.c_int32, P, C.c_size_t, C.POINTER(C.c_int32)]),
+    "hb_seq_close": (I, [P, C.c_uint64]),
     "hb_gguf_describe": (I, [C.c_char_p, C.POINTER(ModelDescC)]),
     "hb_model_load_gguf": (I, [P, C.c_char_p]),
     "hb_gguf_read_tensor": (I, [C.c_char_p, C.c_char_p, P, C.c_size_t, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),

@@ -57,6 +57,17 @@ int hb_model_load_finish(hb_engine* e) { return e ? e->impl.load_finish() : HB_E
 int hb_model_load_random(hb_engine* e, const hb_model_desc* d, uint64_t seed) {
   return (e && d) ? e->impl.load_random(*d, seed) : HB_ERR_INVALID;
 }
+int hb_model_load_begin_stack(hb_engine* e, const hb_stack_desc* d, const hb_layer_desc* layers) {
+  return (e && d && layers) ? e->impl.load_begin_stack(*d, layers) : HB_ERR_INVALID;
+}
+int hb_model_load_random_stack(hb_engine* e, const hb_stack_desc* d, const hb_layer_desc* layers, uint64_t seed) {
+  return (e && d && layers) ? e->impl.load_random_stack(*d, layers, seed) : HB_ERR_INVALID;
+}
+int hb_seq_open(hb_engine* e, uint64_t* id) { return e ? e->impl.seq_open(id) : HB_ERR_INVALID; }
+int hb_seq_step(hb_engine* e, const hb_seq_feed* entries, int32_t n, float* out, size_t cap, int32_t* rows) {
+  return e ? e->impl.seq_step(entries, n, out, cap, rows) : HB_ERR_INVALID;
+}
+int hb_seq_close(hb_engine* e, uint64_t id) { return e ? e->impl.seq_close(id) : HB_ERR_INVALID; }
 int hb_model_load_gguf(hb_engine* e, const char* path) { return e ? e->impl.load_gguf(path) : HB_ERR_INVALID; }
 int hb_gguf_describe(const char* path, hb_model_desc* desc) {
   if (!path || !desc) return HB_ERR_INVALID;

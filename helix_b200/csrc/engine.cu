@@ -155,6 +155,7 @@ void Engine::free_all() {
   fr(model_.arena);
   fr(model_.inv_freq);
   fr(kv_);
+  fr(state_);
   fr(ws_);
   fr(d_step_);
   fr(all_logits_);
@@ -250,6 +251,10 @@ StepLayout Engine::layout(int T, int B, size_t pen_entries) const {
   L.topp = o; o = al16(o + 4 * (size_t)B);
   L.lpw = o; o = al16(o + 4 * (size_t)B);
   L.pen_off = o; o = al16(o + 4 * (size_t)(B + 1));
+  L.sslot = o; o = al16(o + 4 * (size_t)B);   // layer-list decoders: state slot, first position of each entry,
+  L.first = o; o = al16(o + 4 * (size_t)B);
+  L.seqof = o; o = al16(o + 4 * (size_t)T);   // entry of each token, rows whose logits are wanted
+  L.rows = o; o = al16(o + 4 * (size_t)T);
   L.pen = o; o = al16(o + 8 * pen_entries);  // {int32 token; float value} entries, last so no offset depends on their number
   L.total = o;
   return L;
@@ -283,7 +288,12 @@ int Engine::tensor_set(const char* name, const void* host, size_t n) {
   const Placement& p = it->second;
   if (n != p.rows * p.cols) return fail(HB_ERR_INVALID, std::string("tensor size mismatch for ") + name);
   CU(cudaSetDevice(cfg_.device));
-  if (p.mode == 0) {
+  if (p.elem == 4) {  // fp32 arena: bf16 payloads are widened (exactly) on the way in
+    std::vector<uint32_t> wide(n);
+    const uint16_t* src = static_cast<const uint16_t*>(host);
+    for (size_t i = 0; i < n; ++i) wide[i] = (uint32_t)src[i] << 16;
+    CU(cudaMemcpy(p.dst, wide.data(), n * 4, cudaMemcpyHostToDevice));
+  } else if (p.mode == 0) {
     CU(cudaMemcpy(p.dst, host, n * 2, cudaMemcpyHostToDevice));
   } else {
     // gate (mode 1) / up (mode 2) rows interleaved per 128-row block: block t -> rows [t*256 + (mode-1)*128, +128)
@@ -301,6 +311,7 @@ int Engine::tensor_set(const char* name, const void* host, size_t n) {
 
 int Engine::alloc_runtime() {
   const hb_model_desc& d = model_.d;
+  if (is_stack()) return alloc_runtime_stack();
   SmLimitScope sm_scope(cfg_.sm_budget);  // the stream-K plans of the decode GEMMs are cut for this engine's SM share
   t_cap_ = cfg_.max_batched_tokens;
   if (d.arch == HB_ARCH_BERT && cfg_.max_ctx > d.max_pos) cfg_.max_ctx = d.max_pos;
@@ -391,6 +402,7 @@ int Engine::alloc_runtime() {
     uint64_t pages = avail / page_bytes;
     const uint64_t want = (uint64_t)cfg_.max_seqs * max_pages_per_seq_;
     if (pages > want) pages = want;
+    if (cfg_.kv_pool_tokens > 0) pages = std::min<uint64_t>(pages, std::max<uint64_t>((cfg_.kv_pool_tokens + page_ - 1) / page_, max_pages_per_seq_));
     if (pages < (uint64_t)max_pages_per_seq_)
       return fail(HB_ERR_OOM, "memory budget leaves no room for one full-context sequence of KV cache");
     num_pages_ = (int)pages;
@@ -1091,12 +1103,13 @@ void Engine::finish_request(Request* r, ReqState st) {
   // last page first: the LRU then evicts a chain from its tail and the shared root (system prompt) survives longest
   for (auto it = r->pages.rbegin(); it != r->pages.rend(); ++it) drop_page(*it);
   r->pages.clear();
+  drop_slot(r);
   r->state = st;
 }
 
 int Engine::submit(const int32_t* toks, int n, const hb_sampling* sp, uint64_t* id) {
   if (!loaded_) return fail(HB_ERR_STATE, "hb_submit before a model is loaded");
-  if (model_.d.arch != HB_ARCH_LLAMA) return fail(HB_ERR_INVALID, "hb_submit needs a decoder model");
+  if (model_.d.arch != HB_ARCH_LLAMA && !is_stack()) return fail(HB_ERR_INVALID, "hb_submit needs a decoder model");
   if (!toks || n <= 0 || !sp || !id) return fail(HB_ERR_INVALID, "null/empty argument");
   if (cuda_error_.load()) return fail(HB_ERR_CUDA, "engine is in a sticky CUDA error state");
   if (n >= cfg_.max_ctx) return fail(HB_ERR_INVALID, "prompt does not fit context_length");
@@ -1285,16 +1298,28 @@ int Engine::run_prefill(std::vector<Request*>& batch) {
     want_all |= (r->sp.capture & HB_CAPTURE_PROMPT_LOGITS) != 0 && r->prefilled + r->chunk <= (int)r->prompt.size();
     if (i < Bp) paged |= r->prefilled > 0;
   }
-  if (want_all) {
-    if (T > 4096) return fail(HB_ERR_INVALID, "HB_CAPTURE_PROMPT_LOGITS limited to 4096 prompt tokens per step");
-    if (all_logits_rows_ < T) {
+  int n_extra = 0;  // layer-list decoders: rows beyond the entries' last ones whose logits leave the step
+  if (step_driven_)
+    for (Request* r : batch) n_extra += (int)r->want.size();
+  else if (want_all && is_stack())
+    n_extra = T;
+  if (want_all || n_extra > 0) {
+    if (want_all && T > 4096) return fail(HB_ERR_INVALID, "HB_CAPTURE_PROMPT_LOGITS limited to 4096 prompt tokens per step");
+    const int need = std::max(want_all ? T : 0, n_extra);
+    if (all_logits_rows_ < need) {
       if (all_logits_) cudaFree(all_logits_);
       all_logits_ = nullptr;
-      CU(cudaMalloc(&all_logits_, (size_t)T * d.vocab * 4));
-      all_logits_rows_ = T;
+      CU(cudaMalloc(&all_logits_, (size_t)need * d.vocab * 4));
+      all_logits_rows_ = need;
     }
   }
+  step_extra_rows_ = n_extra;
   StepLayout L = layout(T, B);
+  int32_t* sslot = (int32_t*)(h_step_ + L.sslot);
+  int32_t* first = (int32_t*)(h_step_ + L.first);
+  int32_t* seqof = (int32_t*)(h_step_ + L.seqof);
+  int32_t* rows = (int32_t*)(h_step_ + L.rows);
+  int n_rows = 0;
   int32_t* tok = (int32_t*)(h_step_ + L.tokens);
   int32_t* pos = (int32_t*)(h_step_ + L.positions);
   int32_t* slot = (int32_t*)(h_step_ + L.slots);
@@ -1308,14 +1333,19 @@ int Engine::run_prefill(std::vector<Request*>& batch) {
     Request* r = batch[i];
     cu[i] = t;
     const int end = r->prefilled + r->chunk;
+    sslot[i] = r->state_slot;
+    first[i] = r->prefilled;
+    if (step_driven_)
+      for (int32_t w : r->want) rows[n_rows++] = t + w;
     for (int j = r->prefilled; j < end; ++j, ++t) {
       tok[t] = token_at(r, j);  // generated tokens too: decode rows of a mixed step, resumed (preempted) sequences
       pos[t] = j;
       slot[t] = r->pages[j / page_] * page_ + j % page_;
+      seqof[t] = i;
     }
     last[i] = t - 1;
     ctx[i] = end;
-    if (paged || i >= Bp) {
+    if (paged || i >= Bp || is_stack()) {
       const int np = (end + page_ - 1) / page_;
       for (int j = 0; j < np; ++j) pt[(size_t)i * max_pages_per_seq_ + j] = r->pages[j];
     }
@@ -1328,10 +1358,12 @@ int Engine::run_prefill(std::vector<Request*>& batch) {
     attn_flops_ += 4.0 * (n * s + n * n * 0.5) * d.head_dim * d.heads;  // QK^T + PV over the causal trapezoid
   }
   CU(cudaEventRecord(fwd_a_, stream_));
-  int rc = forward_llama(T, B, true, max_len, L, want_all, paged);
+  int rc = is_stack() ? forward_stack(T, B, L, step_driven_ ? (const int32_t*)(d_step_ + L.rows) : nullptr, n_extra, all_logits_,
+                                      !step_driven_)
+                      : forward_llama(T, B, true, max_len, L, want_all, paged);
   if (rc != HB_OK) return rc;
   CU(cudaEventRecord(fwd_b_, stream_));
-  CU(cudaMemcpyAsync(h_sampled_, sampled_, (size_t)B * 4, cudaMemcpyDeviceToHost, stream_));
+  if (!step_driven_) CU(cudaMemcpyAsync(h_sampled_, sampled_, (size_t)B * 4, cudaMemcpyDeviceToHost, stream_));
   CU(cudaStreamSynchronize(stream_));
   {
     float ms = 0.f;
@@ -1376,6 +1408,9 @@ int Engine::run_decode(std::vector<Request*>& batch) {
   for (int i = 0; i < B; ++i) {
     Request* r = batch[i];
     const int p = r->kv_len;
+    ((int32_t*)(h_step_ + L.sslot))[i] = r->state_slot;
+    ((int32_t*)(h_step_ + L.first))[i] = p;
+    ((int32_t*)(h_step_ + L.seqof))[i] = i;
     tok[i] = r->out.back();
     pos[i] = p;
     slot[i] = r->pages[p / page_] * page_ + p % page_;
@@ -1390,7 +1425,10 @@ int Engine::run_decode(std::vector<Request*>& batch) {
   attn_bytes_ = 0;
   for (Request* r : batch) attn_bytes_ += (double)(r->kv_len + 1) * 2.0 * d.kv_heads * d.head_dim * 2.0;
   CU(cudaEventRecord(fwd_a_, stream_));
-  if (cfg_.use_cuda_graphs && !profile_) {
+  if (is_stack()) {  // one forward for every kind of step: a decode step is B one-token entries
+    int rc = forward_stack(B, B, L, nullptr, 0, nullptr, true);
+    if (rc != HB_OK) return rc;
+  } else if (cfg_.use_cuda_graphs && !profile_) {
     const int gkey = B | (step_flags_ << 20);  // filter / penalty / log-probability passes are different kernel sequences
     auto it = graphs_.find(gkey);
     if (it == graphs_.end()) {
@@ -1447,6 +1485,7 @@ void Engine::preempt(Request* v) {
   running_.erase(std::remove(running_.begin(), running_.end(), v), running_.end());
   for (auto it = v->pages.rbegin(); it != v->pages.rend(); ++it) drop_page(*it);
   v->pages.clear();
+  drop_slot(v);  // the recurrent state is recomputed with the pages: the sequence restarts from position 0
   v->kv_len = v->prefilled = v->registered = 0;
   v->chain_key = 0;
   v->in_running = false;
@@ -1481,9 +1520,10 @@ void Engine::ensure_decode_pages() {
 int Engine::step(int* did_work) {
   if (did_work) *did_work = 0;
   if (!loaded_) return fail(HB_ERR_STATE, "hb_step before a model is loaded");
-  if (model_.d.arch != HB_ARCH_LLAMA) return HB_OK;
+  if (model_.d.arch != HB_ARCH_LLAMA && !is_stack()) return HB_OK;
   if (cuda_error_.load()) return fail(HB_ERR_CUDA, "engine is in a sticky CUDA error state");
   std::lock_guard<std::mutex> gg(gpu_mu_);
+  step_driven_ = false;
   CU(cudaSetDevice(cfg_.device));
   SmLimitScope sm_scope(cfg_.sm_budget);
   std::vector<Request*> batch;
@@ -1533,6 +1573,7 @@ int Engine::step(int* did_work) {
         // positions never reach max_ctx (generation stops there), so a sequence never needs more than a full context of pages
         const int total = std::min((n + 1 + page_ - 1) / page_, max_pages_per_seq_);
         if ((int)(running_.size() + batch.size()) >= cfg_.max_seqs) break;
+        if (is_stack() && free_slots_.empty()) break;  // no recurrent-state slot left
         // leading full pages already in the pool (always leave >= 1 token to run: its logits seed the decode)
         std::vector<int32_t> hit;
         uint64_t key = 0;
@@ -1561,6 +1602,7 @@ int Engine::step(int* did_work) {
           r->pages.push_back(pg);
         }
         for (int i = 0; i < need; ++i) r->pages.push_back(take_page());
+        if (is_stack()) r->state_slot = take_slot();  // one per admitted sequence: max_seqs slots, admission stops at max_seqs
         r->prefilled = r->kv_len = (int)hit.size() * page_;
         r->registered = (int)hit.size();
         r->chain_key = key;

@@ -46,10 +46,13 @@ struct Request {
   int preempted = 0;    // times this sequence was evicted and re-queued (pages reclaimed, KV recomputed on re-admission)
   int target = 0;       // tokens that must have K/V before the next token is sampled (prompt [+ generated, after a preemption])
   bool in_running = false;
+  int state_slot = -1;  // recurrent-state slot (layer-list decoders): held from admission to finish / preemption
+  bool driven = false;  // fed by hb_seq_step: never queued, never sampled
+  std::vector<int32_t> want;  // driven: positions of the current portion whose logits the caller asked for
 };
 
 struct StepLayout {
-  size_t tokens, positions, slots, cu, last, ctx, pt, temp, seed, topk, topp, lpw, pen_off, pen, total;
+  size_t tokens, positions, slots, cu, last, ctx, pt, temp, seed, topk, topp, lpw, pen_off, sslot, first, seqof, rows, pen, total;
 };
 enum StepFlags : int { STEP_FILTER = 1, STEP_PENALTY = 2, STEP_LOGPROBS = 4 };
 
@@ -63,6 +66,11 @@ class Engine {
   int tensor_set(const char* name, const void* host_bf16, size_t n);
   int load_finish();
   int load_random(const hb_model_desc& d, uint64_t seed);
+  int load_begin_stack(const hb_stack_desc& d, const hb_layer_desc* layers);
+  int load_random_stack(const hb_stack_desc& d, const hb_layer_desc* layers, uint64_t seed);
+  int seq_open(uint64_t* id);
+  int seq_step(const hb_seq_feed* entries, int n, float* out, size_t cap, int* rows_out);
+  int seq_close(uint64_t id);
   int load_gguf(const char* path);
   int weights_arena(void** p, size_t* bytes);
 
@@ -105,6 +113,18 @@ class Engine {
   int forward_llama(int T, int B, bool prefill, int max_seqlen, const StepLayout& L, bool all_logits, bool paged = false,
                     float* pool_out = nullptr);
   int forward_bert(int T, int B, int max_seqlen, const StepLayout& L, float* d_out);
+  // ---- layer-list decoders (engine_stack.cu)
+  bool is_stack() const { return model_.d.arch == HB_ARCH_RISEPEL; }
+  size_t workspace_bytes_stack() const;
+  int alloc_runtime_stack();
+  // one step over T packed tokens of B entries; logits of the entries' last rows -> logits_ (+ sampling when `sample`);
+  // n_extra > 0: logits of rows extra_rows[0..n_extra) (device indices; null = rows 0..n_extra-1) -> extra_out
+  int forward_stack(int T, int B, const StepLayout& L, const int32_t* extra_rows, int n_extra, float* extra_out, bool sample);
+  // C[M, N] (fp32, row stride ldc) = A . W^T: tcgen05 GEMM when the mode and the strides allow it (A_b16 = bf16 copy of A),
+  // CUDA-core fp32 GEMM otherwise
+  int stack_gemm(const float* A, const bf16* A_b16, int lda, const void* W, int N, int K, float* C, int ldc, int M, const void* bias = nullptr);
+  int take_slot();
+  void drop_slot(Request* r);
   int run_prefill(std::vector<Request*>& batch);
   int run_decode(std::vector<Request*>& batch);
   int decode_splits(int B) const;
@@ -162,6 +182,17 @@ class Engine {
   int32_t token_at(const Request* r, int pos) const {
     return pos < (int)r->prompt.size() ? r->prompt[pos] : r->out[pos - (int)r->prompt.size()];
   }
+  // layer-list decoders: recurrent state slots + latent pool planes inside kv_
+  float* state_ = nullptr;               // [max_seqs][model_.state_floats]
+  std::vector<int32_t> free_slots_;
+  std::vector<size_t> plane_off_;        // byte offset of each latent plane in kv_ ([num_pages][page][row] each)
+  struct StackWs {
+    float *x, *p1, *p2, *cq, *qabs, *ctx, *mo, *y;
+    bf16 *x16, *cq16, *mo16;
+    int ld1, ld2, ldcq, ldqa, ldctx, ldmo;
+  } sk_{};
+  bool step_driven_ = false;             // current step comes from hb_seq_step (no sampling)
+  int step_extra_rows_ = 0;
   uint8_t* ws_ = nullptr;
   size_t ws_bytes_ = 0;
   bf16 *x_ = nullptr, *xn_ = nullptr, *qkv_ = nullptr, *attn_ = nullptr, *h_ = nullptr;

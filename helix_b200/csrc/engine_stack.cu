@@ -1,0 +1,476 @@
+// Layer-list decoders (HB_ARCH_RISEPEL) inside hb::Engine: model load, the latent page pool and recurrent state slots,
+// the step's forward pass and the driven-sequence entry points.  Scheduling, page bookkeeping, the step block, sampling
+// and request records are the engine's own (engine.cu); this file adds what differs from the Llama path:
+//   * the residual stream is fp32 and post-normed; every sublayer reads the stream itself;
+//   * ONE forward serves every step shape: each batch entry is a run of tokens [first, first + n) of a sequence whose
+//     earlier tokens live in the latent pool (attention) and in its state slot (recurrence), so a prompt, a portion of a
+//     prompt and a single decoded token are the same code with different n;
+//   * attention layers cache one latent row per token ([c | k_rot]); a layer may read the rows of an earlier layer;
+//   * recurrent layers keep one fp32 matrix per head in a state slot; an entry that starts at position 0 starts from zero,
+//     so a slot needs no clearing when it changes hands.
+#include "engine.h"
+#include "launch.h"
+
+#include <string.h>
+
+#include <algorithm>
+
+namespace hb {
+
+namespace {
+size_t al256(size_t x) { return (x + 255) & ~size_t(255); }
+int up8(int x) { return (x + 7) / 8 * 8; }
+
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+template <typename T>
+__global__ void fill_uniform_kernel(T* p, size_t n, uint64_t seed, float amp, float mean) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const uint64_t h = mix64(seed ^ (i * 0xD1B54A32D192ED03ull));
+    const float u = (float)(h >> 40) * (1.0f / 16777216.0f) * 2.0f - 1.0f;
+    const float v = __bfloat162float(__float2bfloat16(u * amp + mean));  // bf16-representable in either mode
+    if constexpr (sizeof(T) == 4) p[i] = v; else p[i] = __float2bfloat16(v);
+  }
+}
+}  // namespace
+
+#define CU(expr)                                         \
+  do {                                                   \
+    cudaError_t e_ = (expr);                             \
+    if (e_ != cudaSuccess) return fail_cuda(e_, #expr);  \
+  } while (0)
+#define LAUNCH(expr)                                     \
+  do {                                                   \
+    cudaError_t e_ = (expr);                             \
+    launches_.fetch_add(1, std::memory_order_relaxed);   \
+    if (e_ != cudaSuccess) return fail_cuda(e_, #expr);  \
+  } while (0)
+#define SPAN(cat, work, expr) \
+  do {                        \
+    span_begin(cat, work);    \
+    LAUNCH(expr);             \
+    span_end();               \
+  } while (0)
+
+// ------------------------------------------------------------------ load
+int Engine::load_begin_stack(const hb_stack_desc& sd, const hb_layer_desc* layers) {
+  std::lock_guard<std::mutex> g(gpu_mu_);
+  if (loaded_ || load_open_) return fail(HB_ERR_STATE, "model already loaded on this engine");
+  const std::string why = validate_stack(sd, layers);
+  if (!why.empty()) return fail(HB_ERR_INVALID, "unsupported model description: " + why);
+  CU(cudaSetDevice(cfg_.device));
+  size_t free_b = 0, total_b = 0;
+  CU(cudaMemGetInfo(&free_b, &total_b));
+  budget_ = cfg_.memory_budget_bytes ? cfg_.memory_budget_bytes : (free_b > (1ull << 30) ? free_b - (1ull << 30) : free_b);
+  model_.sd = sd;
+  model_.sl.assign(layers, layers + sd.n_layers);
+  hb_model_desc d{};
+  d.arch = HB_ARCH_RISEPEL;
+  d.hidden = sd.width;
+  d.layers = sd.n_layers;
+  d.vocab = sd.vocab;
+  d.norm_eps = sd.norm_eps;
+  d.max_pos = cfg_.max_ctx;
+  model_.d = d;
+  model_.arena_bytes = arena_bytes_for_stack(sd, layers);
+  if (model_.arena_bytes > budget_) return fail(HB_ERR_OOM, "weights alone exceed the memory budget");
+  if (model_.arena_bytes > free_b) return fail(HB_ERR_OOM, "weights exceed free device memory");
+  CU(cudaMalloc(&model_.arena, model_.arena_bytes));
+  layout_stack(model_);
+  load_open_ = true;
+  return HB_OK;
+}
+
+int Engine::load_random_stack(const hb_stack_desc& sd, const hb_layer_desc* layers, uint64_t seed) {
+  int rc = load_begin_stack(sd, layers);
+  if (rc != HB_OK) return rc;
+  std::lock_guard<std::mutex> g(gpu_mu_);
+  CU(cudaSetDevice(cfg_.device));
+  uint64_t k = 0;
+  for (auto& kv : model_.placements) {
+    const Placement& p = kv.second;
+    const size_t n = p.rows * p.cols;
+    // projections ~ U(+-sqrt(3/in)) so activations keep unit scale through any width; gains at their neutral value
+    const float amp = p.is_norm_gain ? 0.f : (p.is_bias ? 0.1f : sqrtf(3.0f / (float)p.cols));
+    const float mean = p.is_norm_gain ? p.fill : 0.f;
+    const uint64_t sk = seed * 0x9E3779B97F4A7C15ull + (++k) * 0xD1B54A32D192ED03ull + std::hash<std::string>{}(kv.first);
+    if (p.elem == 4) fill_uniform_kernel<float><<<148 * 4, 256, 0, stream_>>>((float*)p.dst, n, sk, amp, mean);
+    else fill_uniform_kernel<bf16><<<148 * 4, 256, 0, stream_>>>(p.dst, n, sk, amp, mean);
+    CU(cudaGetLastError());
+    model_.filled[kv.first] = true;
+  }
+  CU(cudaStreamSynchronize(stream_));
+  int rc2 = alloc_runtime();
+  if (rc2 != HB_OK) return rc2;
+  load_open_ = false;
+  loaded_ = true;
+  return HB_OK;
+}
+
+// ------------------------------------------------------------------ sizing
+size_t Engine::workspace_bytes_stack() const {
+  const hb_stack_desc& sd = model_.sd;
+  const size_t T = t_cap_, W = sd.width;
+  int n1 = 0, n2 = 0, q = 0, qa = 0, cx = 0, mo = 0;
+  for (int i = 0; i < sd.n_layers; ++i) {
+    const hb_layer_desc& l = model_.sl[i];
+    n1 = std::max(n1, model_.sw[i].n_in);
+    n1 = std::max(n1, 2 * l.ff);
+    mo = std::max(mo, std::max(l.heads * l.vdim, l.ff));
+    if (l.mixer == HB_MIXER_GLA) {
+      n2 = std::max(n2, l.heads * l.dim);
+      cx = std::max(cx, l.heads * l.vdim);
+    } else {
+      n2 = std::max(n2, l.heads * (l.dim + l.rot_dim));
+      q = std::max(q, l.q_rank);
+      qa = std::max(qa, l.heads * (l.kv_rank + l.rot_dim));
+      cx = std::max(cx, std::max(l.heads * l.kv_rank, l.heads * l.vdim));
+    }
+  }
+  size_t b = 0;
+  b += 2 * al256(T * W * 4) + al256(T * W * 2);                       // x, y, x16
+  b += al256(T * (size_t)up8(n1) * 4) + al256(T * (size_t)up8(n2) * 4);  // p1, p2
+  b += al256(T * (size_t)up8(q) * 4) + al256(T * (size_t)up8(q) * 2);     // cq, cq16
+  b += al256(T * (size_t)up8(qa) * 4) + 2 * al256(T * (size_t)up8(cx) * 4);  // qabs, ctx (+ per-head value output)
+  b += al256(T * (size_t)up8(mo) * 4) + al256(T * (size_t)up8(mo) * 2);   // mo, mo16
+  b += al256((size_t)cfg_.max_seqs * sd.vocab * 4);                   // logits
+  b += al256((size_t)cfg_.max_seqs * 4);                              // sampled
+  b += al256(sample_scratch_bytes(cfg_.max_seqs, sd.vocab));
+  b += 2 * al256((size_t)cfg_.max_seqs * HB_MAX_LOGPROBS * 4);
+  return b;
+}
+
+int Engine::alloc_runtime_stack() {
+  const hb_stack_desc& sd = model_.sd;
+  cfg_.enable_prefix_cache = 0;  // a page of latent rows does not carry the recurrent layers' state of its prefix
+  cfg_.use_cuda_graphs = 0;
+  t_cap_ = cfg_.max_batched_tokens;
+  b_cap_ = cfg_.max_seqs;
+  max_pages_per_seq_ = (cfg_.max_ctx + page_ - 1) / page_;
+  ws_bytes_ = workspace_bytes_stack();
+  CU(cudaMalloc(&ws_, ws_bytes_));
+  uint8_t* p = ws_;
+  auto take = [&](size_t bytes) {
+    uint8_t* r = p;
+    p += al256(bytes);
+    return r;
+  };
+  const size_t T = t_cap_, W = sd.width;
+  int n1 = 0, n2 = 0, q = 0, qa = 0, cx = 0, mo = 0;
+  for (int i = 0; i < sd.n_layers; ++i) {
+    const hb_layer_desc& l = model_.sl[i];
+    n1 = std::max(n1, std::max(model_.sw[i].n_in, 2 * l.ff));
+    mo = std::max(mo, std::max(l.heads * l.vdim, l.ff));
+    if (l.mixer == HB_MIXER_GLA) {
+      n2 = std::max(n2, l.heads * l.dim);
+      cx = std::max(cx, l.heads * l.vdim);
+    } else {
+      n2 = std::max(n2, l.heads * (l.dim + l.rot_dim));
+      q = std::max(q, l.q_rank);
+      qa = std::max(qa, l.heads * (l.kv_rank + l.rot_dim));
+      cx = std::max(cx, std::max(l.heads * l.kv_rank, l.heads * l.vdim));
+    }
+  }
+  sk_.ld1 = up8(n1); sk_.ld2 = up8(n2); sk_.ldcq = up8(q); sk_.ldqa = up8(qa); sk_.ldctx = up8(cx); sk_.ldmo = up8(mo);
+  sk_.x = (float*)take(T * W * 4);
+  sk_.y = (float*)take(T * W * 4);
+  sk_.x16 = (bf16*)take(T * W * 2);
+  sk_.p1 = (float*)take(T * (size_t)sk_.ld1 * 4);
+  sk_.p2 = (float*)take(T * (size_t)sk_.ld2 * 4);
+  sk_.cq = (float*)take(T * (size_t)sk_.ldcq * 4);
+  sk_.cq16 = (bf16*)take(T * (size_t)sk_.ldcq * 2);
+  sk_.qabs = (float*)take(T * (size_t)sk_.ldqa * 4);
+  sk_.ctx = (float*)take(2 * al256(T * (size_t)sk_.ldctx * 4));
+  sk_.mo = (float*)take(T * (size_t)sk_.ldmo * 4);
+  sk_.mo16 = (bf16*)take(T * (size_t)sk_.ldmo * 2);
+  logits_ = (float*)take((size_t)cfg_.max_seqs * sd.vocab * 4);
+  sampled_ = (int32_t*)take((size_t)cfg_.max_seqs * 4);
+  sample_ws_ = take(sample_scratch_bytes(cfg_.max_seqs, sd.vocab));
+  lp_ids_ = (int32_t*)take((size_t)cfg_.max_seqs * HB_MAX_LOGPROBS * 4);
+  lp_vals_ = (float*)take((size_t)cfg_.max_seqs * HB_MAX_LOGPROBS * 4);
+
+  pen_cap_ = std::min<size_t>((size_t)cfg_.max_seqs * cfg_.max_ctx, size_t(4) << 20);
+  step_bytes_ = layout(t_cap_, b_cap_, pen_cap_).total;
+  CU(cudaMalloc(&d_step_, step_bytes_));
+  CU(cudaMallocHost(&h_step_, step_bytes_));
+  CU(cudaMallocHost(&h_sampled_, (size_t)b_cap_ * 4));
+  CU(cudaMallocHost(&h_lp_ids_, (size_t)cfg_.max_seqs * HB_MAX_LOGPROBS * 4));
+  CU(cudaMallocHost(&h_lp_vals_, (size_t)cfg_.max_seqs * HB_MAX_LOGPROBS * 4));
+
+  // recurrent state: one slot per admissible sequence
+  const size_t state_bytes = (size_t)cfg_.max_seqs * std::max<size_t>(model_.state_floats, 1) * 4;
+  CU(cudaMalloc(&state_, state_bytes));
+  CU(cudaMemsetAsync(state_, 0, state_bytes, stream_));
+  free_slots_.resize(cfg_.max_seqs);
+  for (int i = 0; i < cfg_.max_seqs; ++i) free_slots_[i] = cfg_.max_seqs - 1 - i;
+
+  // latent pool: every plane holds num_pages pages of page_ rows; one page id addresses the same positions in all planes
+  uint64_t page_bytes = 0;
+  for (int r : model_.plane_row) page_bytes += (uint64_t)page_ * r * model_.elem;
+  page_bytes = std::max<uint64_t>(page_bytes, 16);
+  const uint64_t used = model_.arena_bytes + ws_bytes_ + step_bytes_ + state_bytes;
+  if (used >= budget_) return fail(HB_ERR_OOM, "weights + workspace exceed the memory budget");
+  size_t free_b = 0, total_b = 0;
+  CU(cudaMemGetInfo(&free_b, &total_b));
+  uint64_t avail = std::min<uint64_t>(budget_ - used, free_b > (256ull << 20) ? free_b - (256ull << 20) : 0);
+  uint64_t pages = avail / page_bytes;
+  const uint64_t want = (uint64_t)cfg_.max_seqs * max_pages_per_seq_;
+  if (pages > want) pages = want;
+  if (cfg_.kv_pool_tokens > 0) pages = std::min<uint64_t>(pages, std::max<uint64_t>((cfg_.kv_pool_tokens + page_ - 1) / page_, max_pages_per_seq_));
+  if (pages < (uint64_t)max_pages_per_seq_) return fail(HB_ERR_OOM, "memory budget leaves no room for one full-context sequence of cache");
+  num_pages_ = (int)pages;
+  kv_bytes_ = pages * page_bytes;
+  CU(cudaMalloc(&kv_, kv_bytes_));
+  CU(cudaMemsetAsync(kv_, 0, kv_bytes_, stream_));
+  CU(cudaStreamSynchronize(stream_));
+  plane_off_.clear();
+  size_t off = 0;
+  for (int r : model_.plane_row) {
+    plane_off_.push_back(off);
+    off += (size_t)num_pages_ * page_ * r * model_.elem;
+  }
+  pmeta_.assign(num_pages_, PageMeta{});
+  cache_.clear();
+  lru_.clear();
+  free_pages_.resize(num_pages_);
+  for (int i = 0; i < num_pages_; ++i) free_pages_[i] = num_pages_ - 1 - i;
+  return HB_OK;
+}
+
+int Engine::take_slot() {
+  if (free_slots_.empty()) return -1;
+  const int s = free_slots_.back();
+  free_slots_.pop_back();
+  return s;
+}
+void Engine::drop_slot(Request* r) {
+  if (r->state_slot >= 0) free_slots_.push_back(r->state_slot);
+  r->state_slot = -1;
+}
+
+// ------------------------------------------------------------------ forward
+int Engine::stack_gemm(const float* A, const bf16* A16, int lda, const void* Wt, int N, int K, float* C, int ldc, int M, const void* bias) {
+  const bool f32 = model_.sd.compute_f32 != 0;
+  static const bool simt_only = [] { const char* e = getenv("HB_STACK_SIMT"); return e && atoi(e) != 0; }();  // A/B and bring-up
+  const double flops = 2.0 * M * N * K;
+  if (!f32 && !simt_only && A16 && !bias && K % 8 == 0 && lda % 8 == 0 && ldc % 4 == 0 && K >= 64 && N >= 64) {
+    GemmArgs g{A16, lda, (const bf16*)Wt, K, C, ldc, nullptr, 0, nullptr, M, N, K, EPI_F32, 0};
+    SPAN(0, flops, gemm_bf16_tn(stream_, g));
+    return HB_OK;
+  }
+  GemmRtArgs g{A, lda, 0, Wt, K, 1, 0, C, ldc, 0, bias, M, N, K, 1, f32};
+  SPAN(5, flops, gemm_rt(stream_, g));
+  return HB_OK;
+}
+
+int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extra_rows, int n_extra, float* extra_out, bool sample) {
+  const hb_stack_desc& sd = model_.sd;
+  const bool f32 = sd.compute_f32 != 0;
+  const int W = sd.width, V = sd.vocab;
+  const int32_t* tokens = (const int32_t*)(d_step_ + L.tokens);
+  const int32_t* positions = (const int32_t*)(d_step_ + L.positions);
+  const int32_t* slots = (const int32_t*)(d_step_ + L.slots);
+  const int32_t* cu = (const int32_t*)(d_step_ + L.cu);
+  const int32_t* last = (const int32_t*)(d_step_ + L.last);
+  const int32_t* pt = (const int32_t*)(d_step_ + L.pt);
+  const int32_t* sslot = (const int32_t*)(d_step_ + L.sslot);
+  const int32_t* first = (const int32_t*)(d_step_ + L.first);
+  const int32_t* seqof = (const int32_t*)(d_step_ + L.seqof);
+  StackWs& k = sk_;
+  bf16* x16 = f32 ? nullptr : k.x16;
+  bf16* cq16 = f32 ? nullptr : k.cq16;
+  bf16* mo16 = f32 ? nullptr : k.mo16;
+  const double rowb = 4.0 * T * W;
+
+  SPAN(3, rowb, embed_rows_f32(stream_, tokens, model_.s_embed, f32, k.x, x16, T, W));
+  for (int i = 0; i < sd.n_layers; ++i) {
+    const hb_layer_desc& l = model_.sl[i];
+    const StackLayerW& w = model_.sw[i];
+    const int H = l.heads, Dk = l.dim, Dv = l.vdim;
+    // every projection that reads the stream, in one GEMM
+    int rc = stack_gemm(k.x, x16, W, w.w_in, w.n_in, W, k.p1, k.ld1, T);
+    if (rc != HB_OK) return rc;
+    if (l.mixer == HB_MIXER_GLA) {
+      // decay: z = a2 (a1 x) + b -> sigmoid(z)^(1/tau), fp32
+      rc = stack_gemm(k.p1 + w.off_a1, nullptr, k.ld1, w.a2, H * Dk, l.decay_rank, k.p2, k.ld2, T);
+      if (rc != HB_OK) return rc;
+      SPAN(3, 8.0 * T * H * Dk, gla_decay(stream_, k.p2, k.ld2, w.a2b, f32, l.tau, T, H * Dk));
+      GlaArgs a{};
+      a.q = k.p1 + w.off_q; a.k = k.p1 + w.off_k; a.v = k.p1 + w.off_v; a.ld = k.ld1;
+      a.decay = k.p2; a.ldd = k.ld2;
+      a.out = k.ctx; a.ldo = k.ldctx;
+      a.state = state_ + w.state_off; a.slot_stride = (long)model_.state_floats;
+      a.cu = cu; a.first_pos = first; a.slots = sslot;
+      a.B = B; a.H = H; a.Dk = Dk; a.Dv = Dv;
+      a.q_scale = 1.0f / sqrtf((float)Dk);
+      SPAN(6, 4.0 * T * H * Dk * Dv, gla_recurrence(stream_, a));
+      SPAN(3, 12.0 * T * H * Dv, headnorm_silu_gate(stream_, k.ctx, k.ldctx, k.p1 + w.off_g, k.ld1, w.hnorm, f32, sd.norm_eps, k.mo, mo16, T, H, Dv));
+    } else {
+      const int R = l.kv_rank, Dr = l.rot_dim, Q = l.q_rank;
+      uint8_t* plane = (uint8_t*)kv_ + plane_off_[w.cache_plane];
+      LatentPrepArgs pa{};
+      pa.p = k.p1; pa.ldp = k.ld1; pa.q_off = w.off_dq; pa.kv_off = w.off_dkv;
+      pa.wq = w.dq_norm; pa.wkv = w.dkv_norm; pa.f32 = f32; pa.eps = sd.norm_eps;
+      pa.cq = k.cq; pa.cq_b16 = cq16; pa.Q = Q;
+      pa.cache = plane; pa.slots = slots; pa.positions = positions;
+      pa.R = R; pa.Dr = Dr; pa.rope_dims = l.rope_dims; pa.rope_base = l.rope_base; pa.T = T;
+      SPAN(3, 8.0 * T * (Q + R + Dr), latent_prep(stream_, pa));
+      rc = stack_gemm(k.cq, cq16, Q, w.uq, H * (Dk + Dr), Q, k.p2, k.ld2, T);
+      if (rc != HB_OK) return rc;
+      {  // keys are never expanded: q_h is carried into the latent space instead (q_h^T W_uk,h), one product per head
+        GemmRtArgs g{k.p2, k.ld2, (long)(Dk + Dr), w.uk, 1, (long)R, (long)Dk * R, k.qabs, k.ldqa, (long)(R + Dr), nullptr, T, R, Dk, H, f32};
+        SPAN(5, 2.0 * T * H * Dk * R, gemm_rt(stream_, g));
+      }
+      SPAN(3, 8.0 * T * H * Dr, latent_q_rope(stream_, k.p2, k.ld2, k.qabs, k.ldqa, positions, T, H, Dk, Dr, R, l.rope_dims, l.rope_base));
+      LatentAttnArgs aa{};
+      aa.qabs = k.qabs; aa.ldqa = k.ldqa; aa.cache = plane; aa.f32 = f32; aa.sink = w.sink;
+      aa.page_table = pt; aa.max_pages = max_pages_per_seq_; aa.page_size = page_;
+      aa.positions = positions; aa.seq_of = seqof;
+      aa.ctx = k.ctx; aa.ldc = k.ldctx;
+      aa.T = T; aa.H = H; aa.R = R; aa.Dr = Dr; aa.window = l.window; aa.scale = l.scale;
+      SPAN(7, 2.0 * T * H * (double)std::min(l.window, cfg_.max_ctx) * (2.0 * R + Dr), latent_attn(stream_, aa));
+      float* ov = k.ctx + al256((size_t)t_cap_ * k.ldctx * 4) / 4;  // per-head values out of the weighted latent
+      {
+        GemmRtArgs g{k.ctx, k.ldctx, (long)R, w.uv, (long)R, 1, (long)Dv * R, ov, k.ldctx, (long)Dv, nullptr, T, Dv, R, H, f32};
+        SPAN(5, 2.0 * T * H * Dv * R, gemm_rt(stream_, g));
+      }
+      SPAN(3, 12.0 * T * H * Dv, sigmoid_gate(stream_, ov, k.ldctx, k.p1 + w.off_g, k.ld1, k.mo, mo16, T, H * Dv));
+    }
+    rc = stack_gemm(k.mo, mo16, H * Dv, w.wo, W, H * Dv, k.y, W, T);
+    if (rc != HB_OK) return rc;
+    SPAN(3, 3 * rowb, resid_postnorm(stream_, k.x, x16, k.y, W, nullptr, w.norm1, f32, sd.resid_alpha, 1.f, sd.norm_eps, T, W));
+    if (l.ff > 0) {
+      const int F = l.ff;
+      rc = stack_gemm(k.x, x16, W, w.w_gu, 2 * F, W, k.p1, k.ld1, T);
+      if (rc != HB_OK) return rc;
+      const void* bu = (const uint8_t*)w.b_gu + (size_t)F * model_.elem;
+      SPAN(3, 12.0 * T * F, clamped_glu(stream_, k.p1, k.ld1, w.b_gu, bu, f32, l.ff_limit, 1.702f, k.mo, mo16, T, F));
+      rc = stack_gemm(k.mo, mo16, F, w.w_down, W, F, k.y, W, T);
+      if (rc != HB_OK) return rc;
+      SPAN(3, 3 * rowb, resid_postnorm(stream_, k.x, x16, k.y, W, w.b_down, w.norm2, f32, sd.resid_alpha, 1.f, sd.norm_eps, T, W));
+    }
+  }
+  // logits: final norm -> head -> soft cap, for the entries' last rows (sampling) and for the rows asked for
+  auto head = [&](const int32_t* rows, int n, float* out) -> int {
+    for (int r0 = 0; r0 < n; r0 += t_cap_) {  // the normed rows go through the (free) projection buffers, t_cap_ rows at a time
+      const int m = std::min(t_cap_, n - r0);
+      const int32_t* idx = rows ? rows + r0 : nullptr;
+      const float* src = rows ? k.x : k.x + (size_t)r0 * W;
+      LAUNCH(norm_rows_f32(stream_, src, idx, model_.s_final_norm, f32, 1.f, sd.norm_eps, k.y, x16, m, W));
+      int rc = stack_gemm(k.y, x16, W, model_.s_head, V, W, out + (size_t)r0 * V, V, m);
+      if (rc != HB_OK) return rc;
+    }
+    LAUNCH(softcap_rows(stream_, out, (size_t)n * V, sd.logit_softcap));
+    return HB_OK;
+  };
+  if (n_extra > 0) {
+    int rc = head(extra_rows, n_extra, extra_out);
+    if (rc != HB_OK) return rc;
+  }
+  if (sample) {
+    int rc = head(last, B, logits_);
+    if (rc != HB_OK) return rc;
+    return sample_step(B, L);
+  }
+  return HB_OK;
+}
+
+// ------------------------------------------------------------------ driven sequences
+int Engine::seq_open(uint64_t* id) {
+  if (!id) return fail(HB_ERR_INVALID, "null argument");
+  if (!loaded_ || !is_stack()) return fail(HB_ERR_STATE, "driven sequences need a loaded layer-list decoder");
+  if (thread_running_) return fail(HB_ERR_STATE, "driven sequences and the step-loop thread exclude each other");
+  std::lock_guard<std::mutex> g(mu_);
+  const int slot = take_slot();
+  if (slot < 0) return fail(HB_ERR_BUSY, "no free state slot");
+  auto r = std::make_unique<Request>();
+  r->driven = true;
+  r->state_slot = slot;
+  r->state = ReqState::RUNNING;
+  r->id = next_id_++;
+  *id = r->id;
+  reqs_[r->id] = std::move(r);
+  return HB_OK;
+}
+
+int Engine::seq_close(uint64_t id) {
+  std::lock_guard<std::mutex> gg(gpu_mu_);
+  std::lock_guard<std::mutex> g(mu_);
+  auto it = reqs_.find(id);
+  if (it == reqs_.end() || !it->second->driven) return fail(HB_ERR_NOT_FOUND, "unknown sequence id");
+  finish_request(it->second.get(), ReqState::FINISHED);  // pages and state slot go back
+  reqs_.erase(it);
+  return HB_OK;
+}
+
+int Engine::seq_step(const hb_seq_feed* entries, int n, float* out, size_t cap, int* rows_out) {
+  if (rows_out) *rows_out = 0;
+  if (!entries || n <= 0) return fail(HB_ERR_INVALID, "null/empty argument");
+  if (!loaded_ || !is_stack()) return fail(HB_ERR_STATE, "driven sequences need a loaded layer-list decoder");
+  if (thread_running_) return fail(HB_ERR_STATE, "driven sequences and the step-loop thread exclude each other");
+  if (cuda_error_.load()) return fail(HB_ERR_CUDA, "engine is in a sticky CUDA error state");
+  if (n > b_cap_) return fail(HB_ERR_INVALID, "more entries than max_seqs");
+  std::lock_guard<std::mutex> gg(gpu_mu_);
+  CU(cudaSetDevice(cfg_.device));
+  SmLimitScope sm_scope(cfg_.sm_budget);
+  std::vector<Request*> batch;
+  int T = 0, R = 0;
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    int need_pages = 0;
+    for (int i = 0; i < n; ++i) {  // validate everything before anything changes hands
+      const hb_seq_feed& f = entries[i];
+      auto it = reqs_.find(f.seq);
+      if (it == reqs_.end() || !it->second->driven) return fail(HB_ERR_NOT_FOUND, "unknown sequence id");
+      Request* r = it->second.get();
+      if (std::find(batch.begin(), batch.end(), r) != batch.end()) return fail(HB_ERR_INVALID, "a sequence appears twice in one step");
+      if (!f.tokens || f.n_tokens <= 0) return fail(HB_ERR_INVALID, "an entry without tokens");
+      if (f.n_want < 0 || (f.n_want > 0 && !f.want)) return fail(HB_ERR_INVALID, "bad want list");
+      for (int j = 0; j < f.n_tokens; ++j)
+        if (f.tokens[j] < 0 || f.tokens[j] >= model_.d.vocab) return fail(HB_ERR_INVALID, "token id out of range");
+      for (int j = 0; j < f.n_want; ++j)
+        if (f.want[j] < 0 || f.want[j] >= f.n_tokens) return fail(HB_ERR_INVALID, "want index outside the entry");
+      if (r->kv_len + f.n_tokens > cfg_.max_ctx) return fail(HB_ERR_INVALID, "sequence exceeds context_length");
+      need_pages += (r->kv_len + f.n_tokens + page_ - 1) / page_ - (int)r->pages.size();
+      T += f.n_tokens;
+      R += f.n_want;
+      batch.push_back(r);
+    }
+    if (T > t_cap_) return fail(HB_ERR_INVALID, "step exceeds max_batched_tokens");
+    if (need_pages > pages_available()) return fail(HB_ERR_BUSY, "not enough free cache pages");
+    if (out == nullptr ? R > 0 : (size_t)R * model_.d.vocab > cap) return fail(HB_ERR_INVALID, "logits buffer too small");
+    for (int i = 0; i < n; ++i) {
+      const hb_seq_feed& f = entries[i];
+      Request* r = batch[i];
+      r->prompt.insert(r->prompt.end(), f.tokens, f.tokens + f.n_tokens);
+      while ((int)r->pages.size() * page_ < (int)r->prompt.size()) r->pages.push_back(take_page());
+      r->prefilled = r->kv_len;
+      r->chunk = f.n_tokens;
+      r->target = r->kv_len + f.n_tokens;
+      r->want.assign(f.want, f.want + f.n_want);
+    }
+  }
+  step_driven_ = true;
+  step_decode_rows_ = 0;
+  int rc = run_prefill(batch);
+  step_driven_ = false;
+  if (rc != HB_OK) return rc;  // a CUDA failure is sticky; the sequences keep their records for hb_seq_close
+  if (R > 0) CU(cudaMemcpy(out, all_logits_, (size_t)R * model_.d.vocab * 4, cudaMemcpyDeviceToHost));
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    for (Request* r : batch) {
+      r->kv_len += r->chunk;
+      r->prefilled = r->kv_len;
+      r->want.clear();
+    }
+  }
+  if (rows_out) *rows_out = R;
+  return HB_OK;
+}
+
+}  // namespace hb

@@ -236,4 +236,95 @@ cudaError_t dec_resid_rmsnorm(cudaStream_t s, const float* ws, const SkinnyPlan&
 // h[m, t*128+j] = silu(sum[m, t*256+j]) * sum[m, t*256+128+j]
 cudaError_t dec_swiglu(cudaStream_t s, const float* ws, const SkinnyPlan& p, bf16* h, int M, int F, const DepSig* dep = nullptr);
 
+// ==================================================================================================================
+// Mechanisms of hybrid decoder stacks (recurrent + windowed-attention layers on a 32-bit residual stream).
+// Activations between kernels are fp32; weights and cache rows are bf16 or fp32 (`f32` selects the element type of
+// every `const void*` weight / cache argument of a call).  Each launcher optionally writes a bf16 copy of its output
+// for the tensor-core GEMM that consumes it (`*_b16`, may be null).
+// ==================================================================================================================
+
+// C[z][m, n] = sum_k A[z][m, k] * W[z](n, k) (+ bias[n]): CUDA-core fp32 FMA GEMM for shapes or precisions the tcgen05
+// GEMMs do not take (true 32-bit mode, strides that are not 16-byte multiples, per-head batched products).
+// W(n, k) = W[z * w_bs + n * w_sn + k * w_sk]; k runs sequentially inside a thread, so a row's result does not depend on M.
+struct GemmRtArgs {
+  const float* A; long lda; long a_bs;
+  const void* W; long w_sn, w_sk, w_bs;
+  float* C; long ldc; long c_bs;
+  const void* bias;   // [N] of the weight type, or null
+  int M, N, K, batch;
+  bool f32;           // element type of W / bias
+};
+cudaError_t gemm_rt(cudaStream_t s, const GemmRtArgs& a);
+
+// x[t, :] = table[tokens[t], :] as fp32 (+ bf16 copy)
+cudaError_t embed_rows_f32(cudaStream_t s, const int32_t* tokens, const void* table, bool f32, float* x, bf16* x_b16, int T, int W);
+// Post-norm residual step: x[t] <- rmsnorm(alpha * x[t] + y[t] (+ bias)) * (gain_offset + w);  rows of y have stride ldy
+cudaError_t resid_postnorm(cudaStream_t s, float* x, bf16* x_b16, const float* y, long ldy, const void* bias, const void* w,
+                           bool f32, float alpha, float gain_offset, float eps, int T, int W);
+// out[r] = rmsnorm(x[row_index ? row_index[r] : r]) * (gain_offset + w)
+cudaError_t norm_rows_f32(cudaStream_t s, const float* x, const int32_t* row_index, const void* w, bool f32, float gain_offset,
+                          float eps, float* out, bf16* out_b16, int rows, int W);
+// logits <- cap * tanh(logits / cap), in place on [rows, V]
+cudaError_t softcap_rows(cudaStream_t s, float* logits, size_t n, float cap);
+// Clamped gated unit: g = min(G + bg, limit); u = clamp(U + bu, -limit, limit); out = g * sigmoid(act_alpha * g) * (u + 1)
+// with G = gu[t, j], U = gu[t, F + j] (row stride ldg)
+cudaError_t clamped_glu(cudaStream_t s, const float* gu, long ldg, const void* bias_g, const void* bias_u, bool f32, float limit,
+                        float act_alpha, float* out, bf16* out_b16, int T, int F);
+
+// ---- gated linear attention: S_t = diag(decay_t) S_{t-1} + k_t v_t^T,  o_t = S_t^T q_t * q_scale, one fp32 state per
+//      (sequence slot, head).  Step entries are token ranges [cu[b], cu[b+1]) of a packed batch; an entry whose first
+//      position is 0 starts from the zero state, any other from its slot.
+// decay[t, n] = sigmoid(z[t, n] + bias[n])^(1/tau) in fp32, in place on z (row stride ldz)
+cudaError_t gla_decay(cudaStream_t s, float* z, long ldz, const void* bias, bool f32, float tau, int T, int N);
+struct GlaArgs {
+  const float* q; const float* k; const float* v; long ld;   // row stride shared by q / k / v (columns of one projection buffer)
+  const float* decay; long ldd;                               // [T, H*Dk]
+  float* out; long ldo;                                        // [T, H*Dv]
+  float* state; long slot_stride;                              // state + slot * slot_stride -> [H][Dk][Dv] fp32 of this layer
+  const int32_t* cu; const int32_t* first_pos; const int32_t* slots;  // [B+1], [B], [B]
+  int B, H, Dk, Dv;
+  float q_scale;
+};
+cudaError_t gla_recurrence(cudaStream_t s, const GlaArgs& a);
+// out[t, h, :] = rmsnorm(o[t, h, :]) * w[:] * silu(g[t, h, :])   (per-head norm over Dv, gain shared by heads)
+cudaError_t headnorm_silu_gate(cudaStream_t s, const float* o, long ldo, const float* g, long ldg, const void* w, bool f32, float eps,
+                               float* out, bf16* out_b16, int T, int H, int Dv);
+
+// ---- latent attention: the cache keeps, per token, the normed latent c [R] and one rotated key part [Dr] shared by all
+//      heads (row = [c | k_rot], R + Dr elements, page-major: row index = page * page_size + offset).
+// From the fused down-projection p[t] = [dq (Q) | dkv (R + Dr) | ...]: cq = rmsnorm(dq) * wq; c = rmsnorm(dkv[:R]) * wkv and
+// k_rot = rotate(dkv[R:], pos) written to cache row slots[t].  kv_off < 0: the layer reads another layer's cache (no write).
+struct LatentPrepArgs {
+  const float* p; long ldp; int q_off, kv_off;
+  const void* wq; const void* wkv; bool f32;
+  float eps;
+  float* cq; bf16* cq_b16; int Q;
+  void* cache; const int32_t* slots; const int32_t* positions;
+  int R, Dr, rope_dims; float rope_base;
+  int T;
+};
+cudaError_t latent_prep(cudaStream_t s, const LatentPrepArgs& a);
+// qabs[t, h, R:R+Dr] = rotate(q[t, h, Dk:Dk+Dr], pos)   (the absorbed part qabs[t, h, :R] comes from a batched GEMM with W_uk)
+cudaError_t latent_q_rope(cudaStream_t s, const float* q, long ldq, float* qabs, long ldqa, const int32_t* positions, int T, int H,
+                          int Dk, int Dr, int R, int rope_dims, float rope_base);
+// Sliding-window attention of every head over the shared latent rows, softmax with a per-head sink in the denominator:
+// ctx[t, h, :] = sum_j p_j c_j,  p_j = exp(s_j - m) / (sum_i exp(s_i - m) + exp(sink_h - m)),
+// s_j = scale * qabs[t, h] . [c_j | k_rot_j] over 0 <= pos_t - j < window.
+struct LatentAttnArgs {
+  const float* qabs; long ldqa;     // [T, H*(R+Dr)]
+  const void* cache; bool f32;      // [rows][R+Dr]
+  const void* sink;                 // [H] weight type
+  const int32_t* page_table; int max_pages, page_size;
+  const int32_t* positions;         // [T]
+  const int32_t* seq_of;            // [T] batch entry of each token
+  float* ctx; long ldc;             // [T, H*R]
+  int T, H, R, Dr, window;
+  float scale;
+};
+cudaError_t latent_attn(cudaStream_t s, const LatentAttnArgs& a);
+// out = o * sigmoid(g)
+cudaError_t sigmoid_gate(cudaStream_t s, const float* o, long ldo, const float* g, long ldg, float* out, bf16* out_b16, int T, int N);
+// f32 -> bf16 copy of a [T, N] block (row strides lds / ldd)
+cudaError_t to_bf16_rows(cudaStream_t s, const float* src, long lds, bf16* dst, long ldd, int T, int N);
+
 }  // namespace hb

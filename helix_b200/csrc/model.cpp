@@ -161,6 +161,179 @@ static size_t carve(Model* m, const hb_model_desc& d, uint8_t* base) {
   return c.off;
 }
 
+// ------------------------------------------------------------------ layer-list decoders
+std::string validate_stack(const hb_stack_desc& d, const hb_layer_desc* L) {
+  if (!L) return "no layer list";
+  if (d.width <= 0 || d.vocab <= 0 || d.n_layers <= 0) return "non-positive dimension";
+  if (d.vocab % 4) return "vocab must be a multiple of 4 (16-byte rows of the fp32 logits)";
+  if (!(d.norm_eps > 0.f)) return "norm_eps must be positive";
+  for (int i = 0; i < d.n_layers; ++i) {
+    const hb_layer_desc& l = L[i];
+    const std::string at = " (layer " + std::to_string(i) + ")";
+    if (l.heads <= 0 || l.dim <= 0 || l.vdim <= 0) return "non-positive head size" + at;
+    if (l.mixer == HB_MIXER_GLA) {
+      if (l.dim > 128) return "GLA key channels per head > 128 unsupported (register-resident state column)" + at;
+      if (!(l.tau > 0.f) || l.decay_rank <= 0) return "GLA needs tau > 0 and a decay rank" + at;
+    } else if (l.mixer == HB_MIXER_LATENT) {
+      if (l.q_rank <= 0 || l.kv_rank <= 0 || l.rot_dim < 0 || l.window <= 0) return "latent attention sizes" + at;
+      if (l.rope_dims < 0 || l.rope_dims % 2 || l.rope_dims > l.rot_dim) return "rope_dims must be even and <= rot_dim" + at;
+      if (l.rope_dims > 0 && !(l.rope_base > 0.f)) return "rope_base must be positive" + at;
+      if ((size_t)(l.kv_rank + l.rot_dim + l.window + 32) * 4 > 200 * 1024) return "window + latent row exceed the attention kernel's shared memory" + at;
+      if (l.kv_from >= 0) {
+        if (l.kv_from >= i) return "kv_from must name an earlier layer" + at;
+        const hb_layer_desc& s = L[l.kv_from];
+        if (s.mixer != HB_MIXER_LATENT || s.kv_from >= 0) return "kv_from must name a latent layer with its own cache rows" + at;
+        if (s.kv_rank != l.kv_rank || s.rot_dim != l.rot_dim) return "kv_from layer has a different latent row" + at;
+      }
+    } else {
+      return "unknown mixer" + at;
+    }
+    if (l.ff < 0) return "negative ff" + at;
+  }
+  return "";
+}
+
+static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc* L, uint8_t* base) {
+  const size_t es = d.compute_f32 ? 4 : 2;
+  size_t off = 0;
+  auto take = [&](size_t elems) -> uint8_t* {
+    uint8_t* p = base ? base + off : nullptr;
+    off += up(elems * es);
+    return p;
+  };
+  auto put = [&](const std::string& name, uint8_t* dst, size_t row_off, size_t rows, size_t cols, bool gain = false, float fill = 1.f,
+                 bool bias = false) {
+    if (!m) return;
+    Placement p;
+    p.dst = reinterpret_cast<bf16*>(dst ? dst + row_off * cols * es : nullptr);
+    p.rows = rows;
+    p.cols = cols;
+    p.is_norm_gain = gain;
+    p.is_bias = bias;
+    p.fill = fill;
+    p.elem = (int)es;
+    m->placements[name] = p;
+  };
+  const size_t W = d.width, V = d.vocab;
+  uint8_t* embed = take(V * W);
+  put("embed", embed, 0, V, W);
+  if (m) {
+    m->s_embed = embed;
+    m->sw.assign(d.n_layers, StackLayerW{});
+    m->state_floats = 0;
+    m->plane_row.clear();
+    m->elem = (int)es;
+  }
+  std::vector<int> plane_of(d.n_layers, -1);
+  int planes = 0;
+  for (int i = 0; i < d.n_layers; ++i) {
+    const hb_layer_desc& l = L[i];
+    const std::string p = "l" + std::to_string(i) + ".";
+    StackLayerW w;
+    const size_t H = l.heads, Dk = l.dim, Dv = l.vdim;
+    uint8_t* n1 = take(W);
+    put(p + "norm1", n1, 0, W, 1, true, 0.f);
+    w.norm1 = n1;
+    if (l.mixer == HB_MIXER_GLA) {
+      const size_t r = l.decay_rank;
+      w.off_q = 0;
+      w.off_k = (int)(H * Dk);
+      w.off_v = (int)(2 * H * Dk);
+      w.off_g = (int)(2 * H * Dk + H * Dv);
+      w.off_a1 = (int)(2 * H * Dk + 2 * H * Dv);
+      w.n_in = (int)(2 * H * Dk + 2 * H * Dv + r);
+      uint8_t* in = take((size_t)w.n_in * W);
+      w.w_in = in;
+      put(p + "mix.q", in, w.off_q, H * Dk, W);
+      put(p + "mix.k", in, w.off_k, H * Dk, W);
+      put(p + "mix.v", in, w.off_v, H * Dv, W);
+      put(p + "mix.g", in, w.off_g, H * Dv, W);
+      put(p + "mix.a1", in, w.off_a1, r, W);
+      uint8_t* a2 = take(H * Dk * r);
+      uint8_t* a2b = take(H * Dk);
+      uint8_t* hn = take(Dv);
+      uint8_t* o = take(W * H * Dv);
+      put(p + "mix.a2", a2, 0, H * Dk, r);
+      put(p + "mix.a2.b", a2b, 0, H * Dk, 1, false, 1.f, true);
+      put(p + "mix.norm", hn, 0, Dv, 1, true, 1.f);
+      put(p + "mix.o", o, 0, W, H * Dv);
+      w.a2 = a2; w.a2b = a2b; w.hnorm = hn; w.wo = o;
+      if (m) {
+        w.state_off = m->state_floats;
+        m->state_floats += H * Dk * Dv;
+      }
+    } else {
+      const size_t Q = l.q_rank, R = l.kv_rank, Dr = l.rot_dim;
+      const bool own = l.kv_from < 0;
+      w.off_dq = 0;
+      w.off_dkv = own ? (int)Q : -1;
+      w.off_g = (int)(Q + (own ? R + Dr : 0));
+      w.n_in = (int)(w.off_g + H * Dv);
+      uint8_t* in = take((size_t)w.n_in * W);
+      w.w_in = in;
+      put(p + "mix.dq", in, 0, Q, W);
+      if (own) put(p + "mix.dkv", in, Q, R + Dr, W);
+      put(p + "mix.g", in, w.off_g, H * Dv, W);
+      uint8_t* dqn = take(Q);
+      uint8_t* uq = take(H * (Dk + Dr) * Q);
+      uint8_t* dkvn = own ? take(R) : nullptr;
+      uint8_t* uk = take(H * Dk * R);
+      uint8_t* uv = take(H * Dv * R);
+      uint8_t* sink = take(H);
+      uint8_t* o = take(W * H * Dv);
+      put(p + "mix.dq.norm", dqn, 0, Q, 1, true, 1.f);
+      put(p + "mix.uq", uq, 0, H * (Dk + Dr), Q);
+      if (own) put(p + "mix.dkv.norm", dkvn, 0, R, 1, true, 1.f);
+      put(p + "mix.uk", uk, 0, H * Dk, R);
+      put(p + "mix.uv", uv, 0, H * Dv, R);
+      put(p + "mix.sink", sink, 0, H, 1, false, 1.f, true);
+      put(p + "mix.o", o, 0, W, H * Dv);
+      w.dq_norm = dqn; w.uq = uq; w.dkv_norm = dkvn; w.uk = uk; w.uv = uv; w.sink = sink; w.wo = o;
+      if (own) {
+        plane_of[i] = planes++;
+        if (m) m->plane_row.push_back((int)(R + Dr));
+      } else {
+        plane_of[i] = plane_of[l.kv_from];
+      }
+      w.cache_plane = plane_of[i];
+    }
+    if (l.ff > 0) {
+      const size_t Fn = l.ff;
+      uint8_t* n2 = take(W);
+      uint8_t* gu = take(2 * Fn * W);
+      uint8_t* bgu = take(2 * Fn);
+      uint8_t* dn = take(W * Fn);
+      uint8_t* bdn = take(W);
+      put(p + "norm2", n2, 0, W, 1, true, 0.f);
+      put(p + "mlp.gate", gu, 0, Fn, W);
+      put(p + "mlp.up", gu, Fn, Fn, W);
+      put(p + "mlp.gate.b", bgu, 0, Fn, 1, false, 1.f, true);
+      put(p + "mlp.up.b", bgu, Fn, Fn, 1, false, 1.f, true);
+      put(p + "mlp.down", dn, 0, W, Fn);
+      put(p + "mlp.down.b", bdn, 0, W, 1, false, 1.f, true);
+      w.norm2 = n2; w.w_gu = gu; w.b_gu = bgu; w.w_down = dn; w.b_down = bdn;
+    }
+    if (m) m->sw[i] = w;
+  }
+  uint8_t* fn = take(W);
+  uint8_t* head = take(V * W);
+  put("final.norm", fn, 0, W, 1, true, 0.f);
+  put("head", head, 0, V, W);
+  if (m) {
+    m->s_final_norm = fn;
+    m->s_head = head;
+  }
+  return off;
+}
+
+size_t arena_bytes_for_stack(const hb_stack_desc& d, const hb_layer_desc* layers) { return carve_stack(nullptr, d, layers, nullptr); }
+
+void layout_stack(Model& m) {
+  m.placements.clear();
+  m.filled.clear();
+  carve_stack(&m, m.sd, m.sl.data(), reinterpret_cast<uint8_t*>(m.arena));
+}
+
 size_t arena_bytes_for(const hb_model_desc& d) { return carve(nullptr, d, nullptr); }
 
 void layout_model(Model& m) {

@@ -21,6 +21,22 @@ struct BertLayerW {
   bf16 *wqkv, *bqkv, *wo, *bo, *ln1_g, *ln1_b, *w1, *b1, *w2, *b2, *ln2_g, *ln2_b;
 };
 
+// One layer of a layer-list decoder (HB_ARCH_RISEPEL).  Pointers are arena addresses of elements of Model::elem bytes.
+// Projections that read the same input are stacked into one weight (w_in) so one GEMM produces all of them:
+//   GLA:    rows [q | k | v | g | a1]            LATENT: rows [dq | dkv (own cache only) | g]
+struct StackLayerW {
+  void *norm1 = nullptr, *norm2 = nullptr;
+  void* w_in = nullptr;
+  int n_in = 0;
+  int off_q = 0, off_k = 0, off_v = 0, off_g = 0, off_a1 = 0, off_dq = 0, off_dkv = -1;  // columns of the fused projection
+  void *a2 = nullptr, *a2b = nullptr, *hnorm = nullptr;                                          // GLA
+  void *dq_norm = nullptr, *uq = nullptr, *dkv_norm = nullptr, *uk = nullptr, *uv = nullptr, *sink = nullptr;  // LATENT
+  void* wo = nullptr;
+  void *w_gu = nullptr, *b_gu = nullptr, *w_down = nullptr, *b_down = nullptr;  // feed-forward: rows [gate | up]
+  size_t state_off = 0;  // GLA: float offset of this layer's [heads][dim][vdim] block inside a state slot
+  int cache_plane = -1;  // LATENT: plane of the latent pool this layer reads (its own, or the kv_from layer's)
+};
+
 // where an uploaded checkpoint tensor lands inside the arena
 struct Placement {
   bf16* dst = nullptr;
@@ -28,6 +44,8 @@ struct Placement {
   int mode = 0;                // 0: contiguous copy; 1: gate rows -> tile*256 + r%128; 2: up rows -> tile*256+128 + r%128
   bool is_norm_gain = false;   // random init sets these to 1
   bool is_bias = false;        // random init keeps these small
+  int elem = 2;                // bytes per arena element (4: layer-list decoders in fp32 mode; payloads are widened on upload)
+  float fill = 1.0f;           // random init value of norm gains (0 where the stored gain is an offset from one)
 };
 
 struct Model {
@@ -41,6 +59,14 @@ struct Model {
   // bert
   bf16 *word = nullptr, *pos = nullptr, *type = nullptr, *emb_ln_g = nullptr, *emb_ln_b = nullptr;
   std::vector<BertLayerW> bl;
+  // layer-list decoders
+  hb_stack_desc sd{};
+  std::vector<hb_layer_desc> sl;
+  std::vector<StackLayerW> sw;
+  void *s_embed = nullptr, *s_final_norm = nullptr, *s_head = nullptr;
+  size_t state_floats = 0;              // fp32 state of one sequence over all GLA layers
+  std::vector<int> plane_row;           // latent pool planes: elements per cached row (kv_rank + rot_dim)
+  int elem = 2;
   std::unordered_map<std::string, Placement> placements;  // HF checkpoint name -> arena slot
   std::unordered_map<std::string, bool> filled;
 
@@ -49,6 +75,10 @@ struct Model {
 
 // Validates the description against what the kernels support; returns "" when fine.
 std::string validate_desc(const hb_model_desc& d);
+// Layer-list decoders: validation, arena size, layout (fills m.sw, m.placements, m.state_floats, m.plane_row).
+std::string validate_stack(const hb_stack_desc& d, const hb_layer_desc* layers);
+size_t arena_bytes_for_stack(const hb_stack_desc& d, const hb_layer_desc* layers);
+void layout_stack(Model& m);
 // Arena size in bytes for a description (also used by hb_memory_estimate).
 size_t arena_bytes_for(const hb_model_desc& d);
 // Carves `m.arena` (already allocated, m.arena_bytes long) into tensors and fills m.placements.

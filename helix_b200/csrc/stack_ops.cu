@@ -1,0 +1,525 @@
+// Mechanisms of hybrid decoder stacks on a 32-bit residual stream: CUDA-core GEMM for exact / odd-shaped products,
+// post-norm residual step, gated-linear-attention recurrence, windowed latent attention with a softmax sink, clamped
+// gated unit, soft-capped logits.  Everything the recurrence and the softmax touch is fp32; weights and cache rows are
+// bf16 or fp32 (template parameter WT / CT).  Summation orders are fixed per output element and do not depend on the
+// batch a row travels in, so a position's result is the same whatever else the step carries.
+#include <math.h>
+
+#include "kernels.h"
+#include "launch.h"
+
+namespace hb {
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p, size_t i);
+template <> __device__ __forceinline__ float ldf<float>(const float* p, size_t i) { return p[i]; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p, size_t i) { return __bfloat162float(p[i]); }
+template <typename T> __device__ __forceinline__ void stf(T* p, size_t i, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, size_t i, float v) { p[i] = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, size_t i, float v) { p[i] = __float2bfloat16(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// sum over the block; every thread gets the result.  red: >= 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (l < nw) ? red[l] : 0.f;
+  return warp_sum(t);
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (l < nw) ? red[l] : -INFINITY;
+  return warp_max(t);
+}
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-z)); }
+
+// ------------------------------------------------------------------ CUDA-core GEMM
+constexpr int GT = 64, GK = 16;
+template <typename WT>
+__global__ void __launch_bounds__(256) gemm_rt_kernel(const float* __restrict__ A, long lda, long a_bs, const WT* __restrict__ W,
+                                                      long w_sn, long w_sk, long w_bs, float* __restrict__ C, long ldc, long c_bs,
+                                                      const WT* __restrict__ bias, int M, int N, int K) {
+  __shared__ float As[GK][GT + 4];
+  __shared__ float Ws[GK][GT + 4];
+  const int z = blockIdx.z;
+  A += (size_t)z * a_bs;
+  W += (size_t)z * w_bs;
+  C += (size_t)z * c_bs;
+  const int m0 = blockIdx.y * GT, n0 = blockIdx.x * GT;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4] = {};
+  const int lr = threadIdx.x >> 2, lk = (threadIdx.x & 3) * 4;  // loader: row lr of the tile, 4 consecutive k
+  for (int k0 = 0; k0 < K; k0 += GK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = k0 + lk + i;
+      const int m = m0 + lr, n = n0 + lr;
+      As[lk + i][lr] = (m < M && k < K) ? A[(size_t)m * lda + k] : 0.f;
+      Ws[lk + i][lr] = (n < N && k < K) ? ldf<WT>(W, (size_t)n * w_sn + (size_t)k * w_sk) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < GK; ++kk) {
+      float a[4], w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) C[(size_t)m * ldc + n] = acc[i][j] + (bias ? ldf<WT>(bias, n) : 0.f);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ row kernels
+template <typename WT>
+__global__ void embed_rows_kernel(const int32_t* __restrict__ tokens, const WT* __restrict__ table, float* __restrict__ x,
+                                  bf16* __restrict__ xb, int W) {
+  const int t = blockIdx.x;
+  const WT* src = table + (size_t)tokens[t] * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = ldf<WT>(src, i);
+    x[(size_t)t * W + i] = v;
+    if (xb) xb[(size_t)t * W + i] = __float2bfloat16(v);
+  }
+}
+
+// out = rmsnorm(alpha * x + y + bias) * (off + w); y == nullptr: plain norm of x (alpha = 1).  dynamic smem: W floats + 32
+template <typename WT>
+__global__ void __launch_bounds__(256) postnorm_kernel(const float* __restrict__ x, const int32_t* __restrict__ row_index,
+                                                       const float* __restrict__ y, long ldy, const WT* __restrict__ bias,
+                                                       const WT* __restrict__ w, float alpha, float off, float eps,
+                                                       float* __restrict__ out, bf16* __restrict__ outb, int W) {
+  extern __shared__ float sm[];
+  float* row = sm;
+  float* red = sm + W;
+  const int r = blockIdx.x;
+  const size_t src = row_index ? (size_t)row_index[r] : (size_t)r;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float v = x[src * W + i];
+    if (y) v = alpha * v + y[(size_t)r * ldy + i] + (bias ? ldf<WT>(bias, i) : 0.f);
+    row[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float rs = 1.f / sqrtf(ss / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = row[i] * rs * (off + ldf<WT>(w, i));
+    out[(size_t)r * W + i] = v;
+    if (outb) outb[(size_t)r * W + i] = __float2bfloat16(v);
+  }
+}
+
+__global__ void softcap_kernel(float* __restrict__ z, size_t n, float cap) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) z[i] = cap * tanhf(z[i] / cap);
+}
+
+template <typename WT>
+__global__ void clamped_glu_kernel(const float* __restrict__ gu, long ldg, const WT* __restrict__ bg, const WT* __restrict__ bu,
+                                   float limit, float act_alpha, float* __restrict__ out, bf16* __restrict__ outb, int F) {
+  const int t = blockIdx.y;
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= F) return;
+  float g = gu[(size_t)t * ldg + j] + (bg ? ldf<WT>(bg, j) : 0.f);
+  float u = gu[(size_t)t * ldg + F + j] + (bu ? ldf<WT>(bu, j) : 0.f);
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  const float v = g * sigmoidf_(act_alpha * g) * (u + 1.f);
+  out[(size_t)t * F + j] = v;
+  if (outb) outb[(size_t)t * F + j] = __float2bfloat16(v);
+}
+
+__global__ void sigmoid_gate_kernel(const float* __restrict__ o, long ldo, const float* __restrict__ g, long ldg,
+                                    float* __restrict__ out, bf16* __restrict__ outb, int N) {
+  const int t = blockIdx.y;
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= N) return;
+  const float v = o[(size_t)t * ldo + j] * sigmoidf_(g[(size_t)t * ldg + j]);
+  out[(size_t)t * N + j] = v;
+  if (outb) outb[(size_t)t * N + j] = __float2bfloat16(v);
+}
+
+__global__ void to_bf16_kernel(const float* __restrict__ src, long lds, bf16* __restrict__ dst, long ldd, int N) {
+  const int t = blockIdx.y;
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j < N) dst[(size_t)t * ldd + j] = __float2bfloat16(src[(size_t)t * lds + j]);
+}
+
+// ------------------------------------------------------------------ gated linear attention
+template <typename WT>
+__global__ void gla_decay_kernel(float* __restrict__ z, long ldz, const WT* __restrict__ bias, float inv_tau, int N) {
+  const int t = blockIdx.y;
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= N) return;
+  const float v = z[(size_t)t * ldz + j] + (bias ? ldf<WT>(bias, j) : 0.f);
+  // log sigmoid(v) = -softplus(-v), evaluated without overflow on either side
+  const float ls = (v >= 0.f) ? -log1pf(expf(-v)) : v - log1pf(expf(v));
+  z[(size_t)t * ldz + j] = expf(ls * inv_tau);
+}
+
+// One block per (entry, head, slice of value columns); thread j owns column j of the state (DKP >= Dk fp32 registers).
+// Tokens are staged through shared memory TCH at a time: q, k, decay of the head are the same for every thread.
+constexpr int kGlaTch = 8;
+template <int DKP>
+__global__ void __launch_bounds__(128) gla_recurrence_kernel(GlaArgs a) {
+  extern __shared__ float sm[];  // [kGlaTch][3][DKP]
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int j = blockIdx.z * blockDim.x + threadIdx.x;
+  const bool live = j < a.Dv;
+  const int t0 = a.cu[b], t1 = a.cu[b + 1];
+  const int Dk = a.Dk;
+  float* st = a.state + (size_t)a.slots[b] * a.slot_stride + (size_t)h * Dk * a.Dv;
+  float S[DKP];
+  const bool fresh = a.first_pos[b] == 0;
+#pragma unroll
+  for (int i = 0; i < DKP; ++i) S[i] = (!fresh && live && i < Dk) ? st[(size_t)i * a.Dv + j] : 0.f;
+  for (int tc = t0; tc < t1; tc += kGlaTch) {
+    const int nt = min(kGlaTch, t1 - tc);
+    __syncthreads();
+    for (int e = threadIdx.x; e < nt * DKP; e += blockDim.x) {
+      const int tt = e / DKP, i = e % DKP;
+      const size_t row = (size_t)(tc + tt);
+      const bool in = i < Dk;
+      sm[(tt * 3 + 0) * DKP + i] = in ? a.q[row * a.ld + h * Dk + i] : 0.f;
+      sm[(tt * 3 + 1) * DKP + i] = in ? a.k[row * a.ld + h * Dk + i] : 0.f;
+      sm[(tt * 3 + 2) * DKP + i] = in ? a.decay[row * a.ldd + h * Dk + i] : 0.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const size_t row = (size_t)(tc + tt);
+      const float vj = live ? a.v[row * a.ld + (size_t)h * a.Dv + j] : 0.f;
+      const float4* q4 = reinterpret_cast<const float4*>(sm + (tt * 3 + 0) * DKP);
+      const float4* k4 = reinterpret_cast<const float4*>(sm + (tt * 3 + 1) * DKP);
+      const float4* d4 = reinterpret_cast<const float4*>(sm + (tt * 3 + 2) * DKP);
+      float o = 0.f;
+#pragma unroll
+      for (int i = 0; i < DKP / 4; ++i) {
+        const float4 q = q4[i], k = k4[i], d = d4[i];
+        S[4 * i + 0] = fmaf(d.x, S[4 * i + 0], k.x * vj); o = fmaf(S[4 * i + 0], q.x, o);
+        S[4 * i + 1] = fmaf(d.y, S[4 * i + 1], k.y * vj); o = fmaf(S[4 * i + 1], q.y, o);
+        S[4 * i + 2] = fmaf(d.z, S[4 * i + 2], k.z * vj); o = fmaf(S[4 * i + 2], q.z, o);
+        S[4 * i + 3] = fmaf(d.w, S[4 * i + 3], k.w * vj); o = fmaf(S[4 * i + 3], q.w, o);
+      }
+      if (live) a.out[row * a.ldo + (size_t)h * a.Dv + j] = o * a.q_scale;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < DKP; ++i)
+      if (i < Dk) st[(size_t)i * a.Dv + j] = S[i];
+  }
+}
+
+// one warp per (token, head)
+template <typename WT>
+__global__ void headnorm_gate_kernel(const float* __restrict__ o, long ldo, const float* __restrict__ g, long ldg,
+                                     const WT* __restrict__ w, float eps, float* __restrict__ out, bf16* __restrict__ outb, int T,
+                                     int H, int Dv) {
+  const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= T * H) return;
+  const int t = item / H, h = item % H, l = threadIdx.x & 31;
+  const float* src = o + (size_t)t * ldo + (size_t)h * Dv;
+  const float* gs = g + (size_t)t * ldg + (size_t)h * Dv;
+  float ss = 0.f;
+  for (int i = l; i < Dv; i += 32) ss += src[i] * src[i];
+  ss = warp_sum(ss);
+  const float rs = 1.f / sqrtf(ss / (float)Dv + eps);
+  for (int i = l; i < Dv; i += 32) {
+    const float gv = gs[i];
+    const float v = src[i] * rs * ldf<WT>(w, i) * (gv * sigmoidf_(gv));
+    const size_t d = (size_t)t * H * Dv + (size_t)h * Dv + i;
+    out[d] = v;
+    if (outb) outb[d] = __float2bfloat16(v);
+  }
+}
+
+// ------------------------------------------------------------------ latent attention
+// angle of pair i at position p: p * base^(-2i/dims), in fp32
+__device__ __forceinline__ void rope_pair(float u, float v, int pos, int i, int dims, float base, float* ou, float* ov) {
+  const float f = powf(base, -2.f * (float)i / (float)dims);
+  float s, c;
+  sincosf((float)pos * f, &s, &c);
+  *ou = u * c - v * s;
+  *ov = v * c + u * s;
+}
+
+template <typename WT, typename CT>
+__global__ void __launch_bounds__(128) latent_prep_kernel(LatentPrepArgs a) {
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const float* p = a.p + (size_t)t * a.ldp;
+  {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < a.Q; i += blockDim.x) ss += p[a.q_off + i] * p[a.q_off + i];
+    ss = block_sum(ss, red);
+    const float rs = 1.f / sqrtf(ss / (float)a.Q + a.eps);
+    for (int i = threadIdx.x; i < a.Q; i += blockDim.x) {
+      const float v = p[a.q_off + i] * rs * ldf<WT>((const WT*)a.wq, i);
+      a.cq[(size_t)t * a.Q + i] = v;
+      if (a.cq_b16) a.cq_b16[(size_t)t * a.Q + i] = __float2bfloat16(v);
+    }
+  }
+  if (a.kv_off < 0) return;
+  const int slot = a.slots[t];
+  if (slot < 0) return;
+  CT* row = (CT*)a.cache + (size_t)slot * (a.R + a.Dr);
+  const float* kv = p + a.kv_off;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < a.R; i += blockDim.x) ss += kv[i] * kv[i];
+  ss = block_sum(ss, red);
+  const float rs = 1.f / sqrtf(ss / (float)a.R + a.eps);
+  for (int i = threadIdx.x; i < a.R; i += blockDim.x) stf<CT>(row, i, kv[i] * rs * ldf<WT>((const WT*)a.wkv, i));
+  const int half = a.rope_dims / 2, pos = a.positions[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float u, v;
+    rope_pair(kv[a.R + i], kv[a.R + half + i], pos, i, a.rope_dims, a.rope_base, &u, &v);
+    stf<CT>(row, a.R + i, u);
+    stf<CT>(row, a.R + half + i, v);
+  }
+  for (int i = a.rope_dims + threadIdx.x; i < a.Dr; i += blockDim.x) stf<CT>(row, a.R + i, kv[a.R + i]);
+}
+
+__global__ void latent_q_rope_kernel(const float* __restrict__ q, long ldq, float* __restrict__ qabs, long ldqa,
+                                     const int32_t* __restrict__ positions, int H, int Dk, int Dr, int R, int rope_dims, float base) {
+  const int t = blockIdx.x, pos = positions[t], half = rope_dims / 2;
+  for (int e = threadIdx.x; e < H * Dr; e += blockDim.x) {
+    const int h = e / Dr, i = e % Dr;
+    const float* src = q + (size_t)t * ldq + (size_t)h * (Dk + Dr) + Dk;
+    float* dst = qabs + (size_t)t * ldqa + (size_t)h * (R + Dr) + R;
+    if (i < half) {
+      float u, v;
+      rope_pair(src[i], src[half + i], pos, i, rope_dims, base, &u, &v);
+      dst[i] = u;
+      dst[half + i] = v;
+    } else if (i >= rope_dims) {
+      dst[i] = src[i];
+    }
+  }
+}
+
+// One block per (token, head).  dynamic smem: q [R+Dr] + scores [window] + 32.
+template <typename WT, typename CT>
+__global__ void __launch_bounds__(128) latent_attn_kernel(LatentAttnArgs a) {
+  extern __shared__ float sm[];
+  const int D = a.R + a.Dr;
+  float* qs = sm;
+  float* sc = sm + D;
+  float* red = sc + a.window;
+  const int t = blockIdx.x, h = blockIdx.y;
+  const int pos = a.positions[t];
+  const int n = min(pos + 1, a.window), j0 = pos - n + 1;  // keys j0 .. pos
+  const int32_t* pt = a.page_table + (size_t)a.seq_of[t] * a.max_pages;
+  const CT* cache = (const CT*)a.cache;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) qs[i] = a.qabs[(size_t)t * a.ldqa + (size_t)h * D + i];
+  __syncthreads();
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int jj = w; jj < n; jj += nw) {
+    const int j = j0 + jj;
+    const CT* row = cache + ((size_t)pt[j / a.page_size] * a.page_size + j % a.page_size) * D;
+    float s = 0.f;
+    for (int i = l; i < D; i += 32) s = fmaf(qs[i], ldf<CT>(row, i), s);
+    s = warp_sum(s);
+    if (l == 0) sc[jj] = s * a.scale;
+  }
+  __syncthreads();
+  const float sink = ldf<WT>((const WT*)a.sink, h);
+  float m = sink;
+  for (int jj = threadIdx.x; jj < n; jj += blockDim.x) m = fmaxf(m, sc[jj]);
+  m = block_max(m, red);
+  float sum = 0.f;
+  for (int jj = threadIdx.x; jj < n; jj += blockDim.x) {
+    const float e = expf(sc[jj] - m);
+    sc[jj] = e;
+    sum += e;
+  }
+  sum = block_sum(sum, red) + expf(sink - m);  // block_sum's barriers also publish sc[]
+  const float inv = 1.f / sum;
+  for (int r = threadIdx.x; r < a.R; r += blockDim.x) {
+    float acc = 0.f;
+    for (int jj = 0; jj < n; ++jj) {
+      const int j = j0 + jj;
+      const CT* row = cache + ((size_t)pt[j / a.page_size] * a.page_size + j % a.page_size) * D;
+      acc = fmaf(sc[jj], ldf<CT>(row, r), acc);
+    }
+    a.ctx[(size_t)t * a.ldc + (size_t)h * a.R + r] = acc * inv;
+  }
+}
+
+}  // namespace
+
+#define KERR() cudaGetLastError()
+
+cudaError_t gemm_rt(cudaStream_t s, const GemmRtArgs& a) {
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.batch <= 0) return cudaErrorInvalidValue;
+  dim3 grid((a.N + GT - 1) / GT, (a.M + GT - 1) / GT, a.batch);
+  if (a.f32)
+    gemm_rt_kernel<float><<<grid, 256, 0, s>>>(a.A, a.lda, a.a_bs, (const float*)a.W, a.w_sn, a.w_sk, a.w_bs, a.C, a.ldc, a.c_bs,
+                                               (const float*)a.bias, a.M, a.N, a.K);
+  else
+    gemm_rt_kernel<bf16><<<grid, 256, 0, s>>>(a.A, a.lda, a.a_bs, (const bf16*)a.W, a.w_sn, a.w_sk, a.w_bs, a.C, a.ldc, a.c_bs,
+                                              (const bf16*)a.bias, a.M, a.N, a.K);
+  return KERR();
+}
+
+cudaError_t embed_rows_f32(cudaStream_t s, const int32_t* tokens, const void* table, bool f32, float* x, bf16* xb, int T, int W) {
+  if (T <= 0) return cudaSuccess;
+  if (f32) embed_rows_kernel<float><<<T, 128, 0, s>>>(tokens, (const float*)table, x, xb, W);
+  else embed_rows_kernel<bf16><<<T, 128, 0, s>>>(tokens, (const bf16*)table, x, xb, W);
+  return KERR();
+}
+
+static cudaError_t postnorm_launch(cudaStream_t s, const float* x, const int32_t* idx, const float* y, long ldy, const void* bias,
+                                   const void* w, bool f32, float alpha, float off, float eps, float* out, bf16* outb, int rows, int W) {
+  if (rows <= 0) return cudaSuccess;
+  const size_t smem = (size_t)(W + 32) * 4;
+  if (smem > 48 * 1024) {
+    static bool done[2] = {false, false};
+    if (!done[f32]) {
+      cudaError_t e = f32 ? cudaFuncSetAttribute(postnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
+                          : cudaFuncSetAttribute(postnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      if (e != cudaSuccess) return e;
+      done[f32] = true;
+    }
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
+  }
+  if (f32)
+    postnorm_kernel<float><<<rows, 256, smem, s>>>(x, idx, y, ldy, (const float*)bias, (const float*)w, alpha, off, eps, out, outb, W);
+  else
+    postnorm_kernel<bf16><<<rows, 256, smem, s>>>(x, idx, y, ldy, (const bf16*)bias, (const bf16*)w, alpha, off, eps, out, outb, W);
+  return KERR();
+}
+cudaError_t resid_postnorm(cudaStream_t s, float* x, bf16* xb, const float* y, long ldy, const void* bias, const void* w, bool f32,
+                           float alpha, float off, float eps, int T, int W) {
+  if (!y) return cudaErrorInvalidValue;
+  return postnorm_launch(s, x, nullptr, y, ldy, bias, w, f32, alpha, off, eps, x, xb, T, W);
+}
+cudaError_t norm_rows_f32(cudaStream_t s, const float* x, const int32_t* row_index, const void* w, bool f32, float off, float eps,
+                          float* out, bf16* outb, int rows, int W) {
+  return postnorm_launch(s, x, row_index, nullptr, 0, nullptr, w, f32, 1.f, off, eps, out, outb, rows, W);
+}
+
+cudaError_t softcap_rows(cudaStream_t s, float* logits, size_t n, float cap) {
+  if (n == 0 || !(cap > 0.f)) return cudaSuccess;
+  softcap_kernel<<<(unsigned)std::min<size_t>((n + 255) / 256, 148 * 16), 256, 0, s>>>(logits, n, cap);
+  return KERR();
+}
+
+cudaError_t clamped_glu(cudaStream_t s, const float* gu, long ldg, const void* bg, const void* bu, bool f32, float limit,
+                        float act_alpha, float* out, bf16* outb, int T, int F) {
+  if (T <= 0) return cudaSuccess;
+  dim3 grid((F + 255) / 256, T);
+  if (f32) clamped_glu_kernel<float><<<grid, 256, 0, s>>>(gu, ldg, (const float*)bg, (const float*)bu, limit, act_alpha, out, outb, F);
+  else clamped_glu_kernel<bf16><<<grid, 256, 0, s>>>(gu, ldg, (const bf16*)bg, (const bf16*)bu, limit, act_alpha, out, outb, F);
+  return KERR();
+}
+
+cudaError_t sigmoid_gate(cudaStream_t s, const float* o, long ldo, const float* g, long ldg, float* out, bf16* outb, int T, int N) {
+  if (T <= 0) return cudaSuccess;
+  sigmoid_gate_kernel<<<dim3((N + 255) / 256, T), 256, 0, s>>>(o, ldo, g, ldg, out, outb, N);
+  return KERR();
+}
+cudaError_t to_bf16_rows(cudaStream_t s, const float* src, long lds, bf16* dst, long ldd, int T, int N) {
+  if (T <= 0) return cudaSuccess;
+  to_bf16_kernel<<<dim3((N + 255) / 256, T), 256, 0, s>>>(src, lds, dst, ldd, N);
+  return KERR();
+}
+
+cudaError_t gla_decay(cudaStream_t s, float* z, long ldz, const void* bias, bool f32, float tau, int T, int N) {
+  if (T <= 0) return cudaSuccess;
+  dim3 grid((N + 255) / 256, T);
+  if (f32) gla_decay_kernel<float><<<grid, 256, 0, s>>>(z, ldz, (const float*)bias, 1.f / tau, N);
+  else gla_decay_kernel<bf16><<<grid, 256, 0, s>>>(z, ldz, (const bf16*)bias, 1.f / tau, N);
+  return KERR();
+}
+
+template <int DKP>
+static cudaError_t gla_launch(cudaStream_t s, const GlaArgs& a) {
+  const int cols = std::min(128, (a.Dv + 31) / 32 * 32);
+  dim3 grid(a.B, a.H, (a.Dv + cols - 1) / cols);
+  gla_recurrence_kernel<DKP><<<grid, cols, (size_t)kGlaTch * 3 * DKP * 4, s>>>(a);
+  return KERR();
+}
+cudaError_t gla_recurrence(cudaStream_t s, const GlaArgs& a) {
+  if (a.B <= 0) return cudaSuccess;
+  if (a.Dk <= 16) return gla_launch<16>(s, a);
+  if (a.Dk <= 32) return gla_launch<32>(s, a);
+  if (a.Dk <= 64) return gla_launch<64>(s, a);
+  if (a.Dk <= 128) return gla_launch<128>(s, a);
+  return cudaErrorInvalidValue;  // key channels per head beyond the register-resident state column
+}
+
+cudaError_t headnorm_silu_gate(cudaStream_t s, const float* o, long ldo, const float* g, long ldg, const void* w, bool f32, float eps,
+                               float* out, bf16* outb, int T, int H, int Dv) {
+  if (T <= 0) return cudaSuccess;
+  const int items = T * H, grid = (items + 3) / 4;
+  if (f32) headnorm_gate_kernel<float><<<grid, 128, 0, s>>>(o, ldo, g, ldg, (const float*)w, eps, out, outb, T, H, Dv);
+  else headnorm_gate_kernel<bf16><<<grid, 128, 0, s>>>(o, ldo, g, ldg, (const bf16*)w, eps, out, outb, T, H, Dv);
+  return KERR();
+}
+
+cudaError_t latent_prep(cudaStream_t s, const LatentPrepArgs& a) {
+  if (a.T <= 0) return cudaSuccess;
+  if (a.rope_dims % 2 || a.rope_dims > a.Dr) return cudaErrorInvalidValue;
+  if (a.f32) latent_prep_kernel<float, float><<<a.T, 128, 0, s>>>(a);
+  else latent_prep_kernel<bf16, bf16><<<a.T, 128, 0, s>>>(a);
+  return KERR();
+}
+
+cudaError_t latent_q_rope(cudaStream_t s, const float* q, long ldq, float* qabs, long ldqa, const int32_t* positions, int T, int H,
+                          int Dk, int Dr, int R, int rope_dims, float base) {
+  if (T <= 0) return cudaSuccess;
+  latent_q_rope_kernel<<<T, 128, 0, s>>>(q, ldq, qabs, ldqa, positions, H, Dk, Dr, R, rope_dims, base);
+  return KERR();
+}
+
+cudaError_t latent_attn(cudaStream_t s, const LatentAttnArgs& a) {
+  if (a.T <= 0) return cudaSuccess;
+  const size_t smem = (size_t)(a.R + a.Dr + a.window + 32) * 4;
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;
+  if (smem > 48 * 1024) {
+    static bool done[2] = {false, false};
+    if (!done[a.f32]) {
+      cudaError_t e = a.f32 ? cudaFuncSetAttribute(latent_attn_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
+                            : cudaFuncSetAttribute(latent_attn_kernel<bf16, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      if (e != cudaSuccess) return e;
+      done[a.f32] = true;
+    }
+  }
+  dim3 grid(a.T, a.H);
+  if (a.f32) latent_attn_kernel<float, float><<<grid, 128, smem, s>>>(a);
+  else latent_attn_kernel<bf16, bf16><<<grid, 128, smem, s>>>(a);
+  return KERR();
+}
+
+}  // namespace hb

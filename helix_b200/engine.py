@@ -10,7 +10,7 @@ from dataclasses import dataclass, field, asdict
 import numpy as np
 
 from . import _lib
-from ._lib import EngineCfg, ModelDescC, SamplingC, StatsC
+from ._lib import EngineCfg, LayerDescC, ModelDescC, SamplingC, SeqFeedC, StackDescC, StatsC
 
 CAPTURE_STEP_LOGITS = 1
 CAPTURE_PROMPT_LOGITS = 2
@@ -38,11 +38,13 @@ class EngineConfig:
     decode_with_prefill: int = 0  # 1: running sequences decode inside prefill steps (mixed batches)
     fused_decode: int = 0         # 1: decode GEMMs with tile finishers instead of separate row kernels (measured slower)
     mixed_step_tokens: int = 0    # token budget of a step that carries decode rows (0 = 2048)
+    kv_pool_tokens: int = 0       # cap of the cache pool in tokens (0 = max_seqs full contexts)
 
     def to_c(self):
         return EngineCfg(self.device, self.memory_budget_bytes, self.max_seqs, self.max_ctx, self.max_batched_tokens,
                          self.kv_page_size, self.use_cuda_graphs, self.enable_prefix_cache, self.sm_budget,
-                         self.sm_partition, self.stream_priority, self.decode_with_prefill, self.fused_decode, self.mixed_step_tokens)
+                         self.sm_partition, self.stream_priority, self.decode_with_prefill, self.fused_decode, self.mixed_step_tokens,
+                         self.kv_pool_tokens)
 
 
 @dataclass
@@ -71,6 +73,57 @@ class ModelDesc:
                           self.vocab, self.max_pos, self.type_vocab, self.tie_embeddings, self.norm_eps,
                           self.rope_theta, self.rope_factor, self.rope_low_freq_factor, self.rope_high_freq_factor,
                           self.rope_orig_max_pos, self.qkv_bias)
+
+
+MIXER_GLA = 0
+MIXER_LATENT = 1
+
+
+@dataclass
+class LayerDesc:
+    """One layer of a layer-list decoder (hb_layer_desc)."""
+    mixer: int = MIXER_GLA
+    heads: int = 0
+    dim: int = 0
+    vdim: int = 0
+    tau: float = 1.0
+    decay_rank: int = 0
+    q_rank: int = 0
+    kv_rank: int = 0
+    rot_dim: int = 0
+    rope_dims: int = 0
+    window: int = 0
+    kv_from: int = -1
+    rope_base: float = 10000.0
+    scale: float = 1.0
+    ff: int = 0
+    ff_limit: float = 0.0
+
+    def to_c(self):
+        return LayerDescC(self.mixer, self.heads, self.dim, self.vdim, self.tau, self.decay_rank, self.q_rank, self.kv_rank,
+                          self.rot_dim, self.rope_dims, self.window, self.kv_from, self.rope_base, self.scale, self.ff, self.ff_limit)
+
+
+@dataclass
+class StackDesc:
+    """A layer-list decoder (hb_stack_desc + hb_layer_desc[]): arch 2."""
+    width: int = 0
+    vocab: int = 0
+    layers: list = field(default_factory=list)
+    compute_f32: int = 0
+    norm_eps: float = 1e-6
+    resid_alpha: float = 1.0
+    logit_softcap: float = 0.0
+    arch: int = 2
+
+    @property
+    def hidden(self):
+        return self.width
+
+    def to_c(self):
+        arr = (LayerDescC * len(self.layers))(*[l.to_c() for l in self.layers])
+        return StackDescC(self.width, self.vocab, len(self.layers), self.compute_f32, self.norm_eps, self.resid_alpha,
+                          self.logit_softcap), arr
 
 
 @dataclass
@@ -165,13 +218,24 @@ class Engine:
         self.close()
 
     # ---- model load
-    def load_random(self, desc: ModelDesc, seed=0):
-        self._ck(self._l.hb_model_load_random(self._h, C.byref(desc.to_c()), seed))
+    def load_random(self, desc, seed=0):
+        if isinstance(desc, StackDesc):
+            sd, layers = desc.to_c()
+            self._ck(self._l.hb_model_load_random_stack(self._h, C.byref(sd), layers, seed))
+        else:
+            self._ck(self._l.hb_model_load_random(self._h, C.byref(desc.to_c()), seed))
         self.desc = desc
 
-    def load_state_dict(self, desc: ModelDesc, tensors):
+    def load_begin(self, desc):
+        if isinstance(desc, StackDesc):
+            sd, layers = desc.to_c()
+            self._ck(self._l.hb_model_load_begin_stack(self._h, C.byref(sd), layers))
+        else:
+            self._ck(self._l.hb_model_load_begin(self._h, C.byref(desc.to_c())))
+
+    def load_state_dict(self, desc, tensors):
         """tensors: {HF checkpoint name: fp32/bf16-representable ndarray}."""
-        self._ck(self._l.hb_model_load_begin(self._h, C.byref(desc.to_c())))
+        self.load_begin(desc)
         for name, a in tensors.items():
             bits = bf16_bits(a)
             self._ck(self._l.hb_model_tensor_set(self._h, name.encode(), bits.ctypes.data, bits.size))
@@ -266,6 +330,30 @@ class Engine:
                     outs[i] += toks
                     done[i] = fin != 0
         return rids, outs
+
+    # ---- driven sequences: the caller feeds token ids, nothing is sampled (hb_seq_*)
+    def seq_open(self):
+        sid = C.c_uint64()
+        self._ck(self._l.hb_seq_open(self._h, C.byref(sid)))
+        return sid.value
+
+    def seq_close(self, sid):
+        self._ck(self._l.hb_seq_close(self._h, sid))
+
+    def seq_step(self, entries):
+        """entries: [(seq id, tokens, want positions)] -> fp32 [sum(len(want)), vocab]; ONE engine step over all entries."""
+        keep, arr = [], (SeqFeedC * len(entries))()
+        rows = 0
+        for i, (sid, toks, want) in enumerate(entries):
+            t = np.ascontiguousarray(toks, dtype=np.int32)
+            w = np.ascontiguousarray(want, dtype=np.int32)
+            keep += [t, w]
+            arr[i] = SeqFeedC(sid, t.ctypes.data, t.size, w.ctypes.data if w.size else None, w.size)
+            rows += w.size
+        out = np.empty((rows, self.desc.vocab), dtype=np.float32)
+        got = C.c_int32()
+        self._ck(self._l.hb_seq_step(self._h, arr, len(entries), out.ctypes.data if rows else None, out.size, C.byref(got)))
+        return out
 
     # ---- embeddings
     def embed(self, seqs):

@@ -11,7 +11,7 @@ import struct
 
 import numpy as np
 
-from .engine import ModelDesc, bf16_bits
+from .engine import LayerDesc, ModelDesc, StackDesc, bf16_bits, MIXER_GLA, MIXER_LATENT
 
 _DT = {"BF16": (np.uint16, 2), "F16": (np.float16, 2), "F32": (np.float32, 4)}
 _IGNORED = ("pooler.", "embeddings.position_ids", "rotary_emb.inv_freq", "cls.", "visual.")  # visual.: the VL tower (not served)
@@ -66,13 +66,13 @@ def load_safetensors(engine, desc: ModelDesc, paths):
     """Stream every tensor of the checkpoint shards into the engine's weight arena."""
     import ctypes as C
     l, h = engine._l, engine._h
-    engine._ck(l.hb_model_load_begin(h, C.byref(desc.to_c())))
+    engine.load_begin(desc)
     for path in ([paths] if isinstance(paths, (str, os.PathLike)) else paths):
         for name, dt, shape, arr in read_safetensors(path):
             cname = canonical_name(name, desc.arch)
             if any(cname.startswith(p) or p in cname for p in _IGNORED):
                 continue
-            if desc.tie_embeddings and cname == "lm_head.weight":
+            if getattr(desc, "tie_embeddings", 0) and cname == "lm_head.weight":
                 continue
             bits = to_bf16_bits(dt, arr)
             engine._ck(l.hb_model_tensor_set(h, cname.encode(), bits.ctypes.data, bits.size))
@@ -80,11 +80,58 @@ def load_safetensors(engine, desc: ModelDesc, paths):
     engine.desc = desc
 
 
-def desc_from_hf_config(cfg):
-    """HF config.json (dict or path) -> ModelDesc: Llama- and Qwen2-family decoders, BERT-family encoders."""
+def safetensors_shapes(paths):
+    """{tensor name: shape} from the headers alone."""
+    out = {}
+    for path in ([paths] if isinstance(paths, (str, os.PathLike)) else paths):
+        with open(path, "rb") as f:
+            n = struct.unpack("<Q", f.read(8))[0]
+            for name, meta in json.loads(f.read(n)).items():
+                if name != "__metadata__":
+                    out[name] = tuple(meta["shape"])
+    return out
+
+
+def risepel_desc(cfg, shapes=None, compute_f32=False):
+    """config.json of a Risepel checkpoint -> StackDesc.  Every size comes from the configuration; the inner size of the
+    decay projection is not a configuration key and is read from the checkpoint's tensor shapes (`l<i>.mix.a1`)."""
+    layers = []
+    for i, ly in enumerate(cfg["layers"]):
+        m = ly["mixer"]
+        mlp = ly.get("mlp")
+        if mlp is not None and mlp.get("kind") != "dense":
+            raise ValueError(f"layer {i}: unsupported feed-forward kind {mlp.get('kind')!r}")
+        d = LayerDesc(heads=m["heads"], dim=m["dim"], vdim=m["vdim"], ff=mlp["ff"] if mlp else 0,
+                      ff_limit=float(mlp["limit"]) if mlp else 0.0)
+        if ly["type"] == "gla":
+            d.mixer, d.tau = MIXER_GLA, float(m["tau"])
+            if shapes is None or f"l{i}.mix.a1" not in shapes:
+                raise ValueError(f"layer {i}: the decay rank needs the checkpoint's tensor shapes")
+            d.decay_rank = int(shapes[f"l{i}.mix.a1"][0])
+        elif ly["type"] == "latent_attention":
+            d.mixer = MIXER_LATENT
+            d.q_rank, d.kv_rank, d.rot_dim = m["q_rank"], m["kv_rank"], m["rot_dim"]
+            d.rope_dims, d.rope_base = int(m["rot"]["dims"]), float(m["rot"]["base"])
+            d.window, d.scale = int(m["mask"]["size"]), float(m["scale"])
+            d.kv_from = int(m["kv_from"]) if m.get("kv_from") is not None else -1
+        else:
+            raise ValueError(f"layer {i}: unknown layer type {ly['type']!r}")
+        layers.append(d)
+    return StackDesc(width=cfg["width"], vocab=cfg["vocab"], layers=layers, compute_f32=int(bool(compute_f32)),
+                     norm_eps=float(cfg["norm"]["eps"]), resid_alpha=float(cfg["postln_alpha"]),
+                     logit_softcap=float(cfg.get("logit_softcap") or 0.0))
+
+
+def desc_from_hf_config(cfg, shapes=None, compute_f32=False):
+    """config.json (dict or path) -> ModelDesc (Llama- and Qwen2-family decoders, BERT-family encoders) or StackDesc
+    (layer-list decoders: "architecture": "Risepel"; `shapes` = safetensors_shapes of the checkpoint)."""
     if not isinstance(cfg, dict):
         with open(cfg) as f:
             cfg = json.load(f)
+    if cfg.get("architecture") == "Risepel":
+        return risepel_desc(cfg, shapes, compute_f32)
+    if compute_f32:
+        raise ValueError("fp32 compute exists for layer-list decoders only")
     mt = cfg.get("model_type", "")
     if mt in ("qwen2", "qwen2_vl") and "text_config" in cfg:  # VL checkpoints nest the language model's configuration
         cfg = dict(cfg["text_config"], model_type="qwen2")

@@ -58,7 +58,12 @@ typedef enum hb_status {
   HB_ERR_BUSY = -6,      /* queue full / no KV pages: retry later */
 } hb_status;
 
-typedef enum hb_arch { HB_ARCH_LLAMA = 0, HB_ARCH_BERT = 1 } hb_arch;
+typedef enum hb_arch {
+  HB_ARCH_LLAMA = 0,
+  HB_ARCH_BERT = 1,
+  HB_ARCH_RISEPEL = 2 /* layer-list decoders (hb_stack_desc + hb_layer_desc[]): recurrent and windowed-attention mixers on a
+                         32-bit post-norm residual stream; loaded with hb_model_load_begin_stack */
+} hb_arch;
 
 typedef struct hb_engine hb_engine;
 
@@ -89,6 +94,9 @@ typedef struct hb_engine_cfg {
                                    Measured slower than the separate row kernels on B200, so off by default */
   int32_t mixed_step_tokens;    /* token budget of a step that carries decode rows (decode_with_prefill): a long prompt
                                    is spread over steps of this size so inter-token latency stays bounded; 0 = 2048 */
+  int32_t kv_pool_tokens;       /* cap of the cache pool in tokens (rounded up to whole pages); 0 = max_seqs full contexts.
+                                   A pool smaller than that makes sequences share it: pages are handed out on demand and
+                                   reused as soon as their sequence ends */
 } hb_engine_cfg;
 
 typedef struct hb_model_desc {
@@ -106,6 +114,41 @@ typedef struct hb_model_desc {
                           model MrLight/dse-qwen2-2b-mrl-v1, api/pkg/model/models.go:421-433); everything else as Llama */
   int32_t reserved[7];
 } hb_model_desc;
+
+/* ---- layer-list decoders (HB_ARCH_RISEPEL).  The stack is described layer by layer; every size and constant is a field, the
+ *      kernels take them as parameters.  Mixers:
+ *        HB_MIXER_GLA     gated linear attention: per head S_t = diag(decay_t) S_{t-1} + k_t v_t^T, o_t = S_t^T q_t / sqrt(dim),
+ *                         decay = sigmoid(low-rank projection + bias)^(1/tau) per key channel, per-head RMS norm of o,
+ *                         silu output gate.  One fp32 state [heads][dim][vdim] per sequence (a state slot, not cache pages).
+ *        HB_MIXER_LATENT  attention over a cached low-rank latent: queries through their own latent (q_rank), keys/values
+ *                         expanded from a shared latent (kv_rank) plus one rotary key part (rot_dim) shared by all heads;
+ *                         sliding window, learned per-head sink in the softmax denominator, sigmoid output gate.  kv_from >= 0:
+ *                         the layer has no down-projection of its own and reads the cache rows of that earlier layer.
+ *      A layer is x <- norm(alpha x + mixer(x)) and, when ff > 0, x <- norm(alpha x + ff(x)) with the clamped gated unit
+ *      g = min(gate, limit), u = clamp(up, +-limit), y = g sigmoid(1.702 g) (u + 1).  Norm gains are stored as offsets from 1.
+ *      Logits are soft-capped: cap * tanh(z / cap) (cap <= 0: off).  Tensor names: embed, final.norm, head, l<i>.norm1/2,
+ *      l<i>.mix.{q,k,v,g,o,norm,a1,a2,a2.b | dq,dq.norm,uq,dkv,dkv.norm,uk,uv,sink,g,o}, l<i>.mlp.{gate,up,down}[.b]. ---- */
+typedef enum hb_mixer { HB_MIXER_GLA = 0, HB_MIXER_LATENT = 1 } hb_mixer;
+typedef struct hb_layer_desc {
+  int32_t mixer;       /* hb_mixer */
+  int32_t heads, dim, vdim;
+  float tau;           /* GLA: decay temperature */
+  int32_t decay_rank;  /* GLA: inner size of the decay projection (rows of a1) */
+  int32_t q_rank, kv_rank, rot_dim; /* LATENT */
+  int32_t rope_dims;   /* leading entries of the rot_dim part that rotate (rotate-half pairing i <-> i + rope_dims/2) */
+  int32_t window;      /* position i sees j with 0 <= i - j < window */
+  int32_t kv_from;     /* < 0: own cache rows */
+  float rope_base, scale;
+  int32_t ff;          /* 0: the layer has no feed-forward sublayer */
+  float ff_limit;
+  int32_t reserved[4];
+} hb_layer_desc;
+typedef struct hb_stack_desc {
+  int32_t width, vocab, n_layers;
+  int32_t compute_f32; /* 1: weights, cache rows and every product in true fp32 (CUDA-core FMA; the exact mode) */
+  float norm_eps, resid_alpha, logit_softcap;
+  int32_t reserved[5];
+} hb_stack_desc;
 
 typedef struct hb_sampling {
   float temperature;   /* <= 0: greedy argmax. (The runner forces 0.1 when a request carries 0:
@@ -185,6 +228,10 @@ int hb_model_load_begin(hb_engine* e, const hb_model_desc* desc);
 int hb_model_tensor_set(hb_engine* e, const char* name, const void* host_bf16, size_t n_elems);
 int hb_model_load_finish(hb_engine* e);
 int hb_model_load_random(hb_engine* e, const hb_model_desc* desc, uint64_t seed);
+/* layer-list decoders: the same begin / tensor_set / finish protocol (tensor_set takes bf16 payloads; with compute_f32 they
+ * are widened on upload), or random weights for benchmarks */
+int hb_model_load_begin_stack(hb_engine* e, const hb_stack_desc* desc, const hb_layer_desc* layers);
+int hb_model_load_random_stack(hb_engine* e, const hb_stack_desc* desc, const hb_layer_desc* layers, uint64_t seed);
 /* ---- GGUF (llama.cpp / Ollama blobs, the format of the reference's default catalogue, e.g. "llama3:instruct" = 8B Q4_0:
  *      api/pkg/model/models.go:259-266): metadata -> description, tensors dequantised to bf16 (F32 F16 BF16 Q8_0 Q4_0 Q4_1
  *      Q5_0 Q5_1 Q4_K Q5_K Q6_K), llama.cpp's q/k row permutation undone.  hb_gguf_read_tensor returns one tensor as fp32 in
@@ -224,6 +271,23 @@ int hb_cancel(hb_engine* e, uint64_t req_id);
 int hb_release(hb_engine* e, uint64_t req_id); /* drop a finished request's record */
 /* parity tap: rows captured for req (see HB_CAPTURE_*), fp32 [rows][vocab] */
 int hb_captured_logits(hb_engine* e, uint64_t req_id, int32_t which, float* out, size_t cap_floats, int32_t* rows);
+
+/* ---- driven sequences (trace replay, teacher forcing, scoring): the caller feeds token ids, nothing is sampled.  One
+ *      hb_seq_step call is ONE engine step over all its entries — portions of several tokens beside single tokens — through
+ *      the same batch layout, forward pass, cache pages and state slots the generation path uses.  A sequence keeps its pages
+ *      and state slot from hb_seq_open to hb_seq_close.  logits_out receives, in entry order, the fp32 rows of the positions
+ *      `want` names (indices into the entry's tokens).  HB_ERR_BUSY: no free state slot / not enough free pages.
+ *      Engines running the step-loop thread refuse these calls; layer-list decoders only. ---- */
+typedef struct hb_seq_feed {
+  uint64_t seq;
+  const int32_t* tokens;
+  int32_t n_tokens;
+  const int32_t* want;
+  int32_t n_want;
+} hb_seq_feed;
+int hb_seq_open(hb_engine* e, uint64_t* seq_id);
+int hb_seq_step(hb_engine* e, const hb_seq_feed* entries, int32_t n_entries, float* logits_out, size_t cap_floats, int32_t* rows_out);
+int hb_seq_close(hb_engine* e, uint64_t seq_id);
 
 /* rows [first_row, first_row + max_rows) of the request's log-probability record (hb_sampling.logprobs = width):
  * ids / logprobs are [rows][width], column 0 = the sampled token, columns 1.. = the most likely tokens in descending
