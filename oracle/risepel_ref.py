@@ -116,7 +116,7 @@ def dense_ff(h, p, limit):
 
 
 def softcap(z, cap):
-    return cap * np.tanh(z / cap)
+    return cap * np.tanh(z / cap) if cap else z  # no cap configured: plain logits
 
 
 # ------------------------------------------------------------------ the model
@@ -170,7 +170,7 @@ class RisepelOracle:
                 taps.append(x.copy())
         st["pos"] += T
         z = norm_offset_gain(x, self.sd["final.norm"], eps) @ self.sd["head"].T
-        return softcap(z, cfg["logit_softcap"])
+        return softcap(z, cfg.get("logit_softcap"))
 
     def greedy(self, prompt, n):
         st = self.new_state()
