@@ -16,7 +16,7 @@ cache.  tokens = sessions * (seq + decode).
                  oracle port on all host threads (pinned with threadpoolctl), bounded sample; --cpu-impl hf switches to
                  HF transformers on torch CPU, which measured 30x slower on the GPU box (profiles/r02c_reference_hf.json)
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload llama8b|bge|pack]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload llama8b|bge|pack|risepel]
 """
 import argparse
 import json
@@ -388,6 +388,66 @@ def bench_bge(args):
     e.close()
 
 
+def bench_risepel(args):
+    """--workload risepel: prefill and decode throughput of Risepel-design stacks (helix_b200.configs.risepel_stack, random
+    weights, bf16 serving mode) at a few layer sizes, beside a Llama-family model of equal width / depth / feed-forward size
+    through the same engine API.  Per size: `sessions` prompts of `seq` tokens + `decode` generated tokens each; tokens/s =
+    tokens / device time of the forward passes of each phase; `families` = CUDA-event spans of one profiled pass by kernel
+    family with achieved FLOP/s or B/s."""
+    import helix_b200 as hb
+    from helix_b200 import configs
+    peaks = measured_peaks()
+    sizes = [(1024, 12), (2048, 12), (4096, 6)] if not args.risepel_sizes else [tuple(int(v) for v in x.split("x")) for x in args.risepel_sizes]
+    sessions, seq, decode = args.sessions, args.seq, args.decode
+    rows = []
+    sampler = ClockSampler(0)
+    sampler.start()
+    for width, layers in sizes:
+        ff = 4 * width
+        row = {"width": width, "layers": layers, "ff": ff}
+        for name, desc in (("risepel", configs.risepel_stack(width, layers, ff=ff)), ("llama", configs.llama_like(width, layers, ff))):
+            e = hb.Engine(hb.EngineConfig(device=0, max_seqs=sessions, max_ctx=seq + decode + 64,
+                                          max_batched_tokens=args.max_batched_tokens, use_cuda_graphs=0 if args.no_graphs else 1))
+            e.load_random(desc, 3)
+            prompts = [session_prompt(i, seq, desc.vocab) for i in range(sessions)]
+            for _ in range(max(1, args.warmup)):
+                serve_once(e, hb, prompts[:max(1, sessions // 4)], 4)
+            s0 = e.stats()
+            for _ in range(args.steps):
+                serve_once(e, hb, prompts, decode)
+            s1 = e.stats()
+            pre_ms, dec_ms = s1["gpu_ms_prefill"] - s0["gpu_ms_prefill"], s1["gpu_ms_decode"] - s0["gpu_ms_decode"]
+            pre_tok, dec_tok = s1["tokens_prefill"] - s0["tokens_prefill"], s1["tokens_decode"] - s0["tokens_decode"]
+            e.set_profile(True)
+            p0 = e.stats()
+            serve_once(e, hb, prompts, min(decode, 16))
+            p1 = e.stats()
+            e.set_profile(False)
+            fam = {}
+            for i, (label, unit) in enumerate((("gemm_tcgen05_prefill", "TFLOP/s"), ("attention_prefill", "TFLOP/s"), ("attention_decode", "GB/s"),
+                                               ("row_kernels", "GB/s"), ("gemm_decode", "GB/s"), ("gemm_cuda_core", "TFLOP/s"),
+                                               ("gla_recurrence", "TFLOP/s"), ("latent_attention", "TFLOP/s"))):
+                ms = p1["prof_ms"][i] - p0["prof_ms"][i]
+                if ms <= 0:
+                    continue
+                w = p1["prof_work"][i] - p0["prof_work"][i]
+                fam[label] = {"ms": round(ms, 3), "launches": p1["prof_launches"][i] - p0["prof_launches"][i],
+                              unit: round(w / (ms * 1e-3) / (1e12 if unit[0] == "T" else 1e9), 2)}
+            row[name] = {"weights_gb": round(s1["weights_bytes"] / 1e9, 3), "prefill_tok_s": round(pre_tok / (pre_ms * 1e-3), 1),
+                         "decode_tok_s": round(dec_tok / (dec_ms * 1e-3), 1), "decode_ms_per_step": round(dec_ms / max(1, s1["steps_decode"] - s0["steps_decode"]), 3),
+                         "launches": int(s1["kernel_launches"] - s0["kernel_launches"]), "families": fam}
+            e.close()
+        rows.append(row)
+    clocks = sampler.stop()
+    line = {"metric": "tokens/sec Risepel-design stacks vs Llama-family at equal width/depth/ff (prefill, decode)", "unit": "tokens/s",
+            "value": rows[0]["risepel"]["prefill_tok_s"], "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
+            "dtype": "bf16", "data": "synthetic", "vs_baseline": None,
+            "config": {"workload": f"{sessions} sessions x ({seq} prompt + {decode} decode) tokens per size, random-init, paged cache (page 64)",
+                       "l2": "weights of every size exceed the 126 MB L2; prompts differ per session"},
+            "peaks": peaks, "sizes": rows, "clocks": clocks}
+    print(json.dumps(line), flush=True)
+
+
 def bge_cpu_baseline(chunks=16):
     """The numpy fp32 oracle (oracle/bert_ref.py) on all host threads over a bounded sample of the same workload."""
     threads = host_threads()
@@ -515,7 +575,8 @@ def main():
     ap.add_argument("--mixed-step-tokens", type=int, default=512)
     ap.add_argument("--fixed-total-sessions", type=int, default=256)
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model (INVALID as a bench number)")
-    ap.add_argument("--workload", default="llama8b", choices=["llama8b", "bge", "pack"])
+    ap.add_argument("--workload", default="llama8b", choices=["llama8b", "bge", "pack", "risepel"])
+    ap.add_argument("--risepel-sizes", nargs="*", default=[], help="risepel workload: WIDTHxLAYERS ... (default 1024x12 2048x12 4096x6)")
     ap.add_argument("--chunks", type=int, default=100000)
     ap.add_argument("--ragged", action="store_true", help="bge workload: chunk lengths U[64,512] instead of 512")
     ap.add_argument("--pack-seconds", type=float, default=8.0)
@@ -529,9 +590,9 @@ def main():
     if args.impl == "reference":
         reference_arm(args, rank, world)
         return
-    if args.workload in ("bge", "pack"):
+    if args.workload in ("bge", "pack", "risepel"):
         if rank == 0:
-            (bench_bge if args.workload == "bge" else bench_pack)(args)
+            {"bge": bench_bge, "pack": bench_pack, "risepel": bench_risepel}[args.workload](args)
         return
 
     import torch

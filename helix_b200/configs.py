@@ -45,3 +45,36 @@ def tiny_qwen2(layers=2, vocab=1000):
 def tiny_bert(layers=2, vocab=1000):
     return ModelDesc(arch=BERT, hidden=256, layers=layers, heads=4, kv_heads=4, head_dim=64, ffn=512, vocab=vocab,
                      max_pos=512, type_vocab=2, norm_eps=1e-12)
+
+
+def risepel_stack(width, layers, ff=None, window=512, pattern=("gla", "gla", "latent"), vocab=32768, compute_f32=False):
+    """A Risepel-design stack at sizes that resemble a served model's layers (random-init benchmarks): per width, heads of
+    128 value channels; GLA layers with 64 key channels per head and a rank-64 decay projection; latent-attention layers with
+    a 512-wide cache latent, 64 rotary dims, queries through a width/4 latent, a sliding window, a feed-forward after every
+    attention layer (the pattern of the design's checkpoints: two recurrent layers, then attention + feed-forward, with
+    every second attention layer reading the cache rows of the one before)."""
+    from .engine import LayerDesc, StackDesc, MIXER_GLA, MIXER_LATENT
+    heads = max(1, width // 128)
+    ff = ff or (width * 4)
+    out, lat_seen, last_own = [], 0, -1
+    for i in range(layers):
+        kind = pattern[i % len(pattern)]
+        if kind == "gla":
+            out.append(LayerDesc(mixer=MIXER_GLA, heads=heads, dim=64, vdim=128, tau=16.0, decay_rank=64))
+        else:
+            share = lat_seen % 2 == 1
+            out.append(LayerDesc(mixer=MIXER_LATENT, heads=heads, dim=128, vdim=128, q_rank=max(64, width // 4), kv_rank=512,
+                                 rot_dim=64, rope_dims=64, window=window, kv_from=last_own if share else -1, rope_base=1e6,
+                                 scale=(128 + 64) ** -0.5, ff=ff, ff_limit=7.0))
+            if not share:
+                last_own = i
+            lat_seen += 1
+    return StackDesc(width=width, vocab=vocab, layers=out, compute_f32=int(compute_f32), norm_eps=1e-6, resid_alpha=2.0,
+                     logit_softcap=30.0)
+
+
+def llama_like(width, layers, ff, vocab=32768):
+    """The closest existing decoder at equal width / depth / feed-forward size (comparison arm of the Risepel benchmark)."""
+    heads = max(1, width // 128)
+    return ModelDesc(arch=LLAMA, hidden=width, layers=layers, heads=heads, kv_heads=max(1, heads // 4), head_dim=128, ffn=ff,
+                     vocab=vocab, max_pos=8192, tie_embeddings=0, norm_eps=1e-5, rope_theta=500000.0)

@@ -113,6 +113,25 @@ int Engine::load_random_stack(const hb_stack_desc& sd, const hb_layer_desc* laye
 }
 
 // ------------------------------------------------------------------ sizing
+// fp32 partial slabs of the weight-streaming GEMM that serves steps of <= 256 tokens (every projection it may be given)
+static size_t stack_skinny_floats(const Model& m) {
+  size_t f = 0;
+  auto shape = [&](size_t N, size_t K) { f = std::max(f, (size_t)gemm_skinny_max_segs((int)N, (int)K, 148) * 256 * N); };
+  const size_t W = m.sd.width;
+  for (int i = 0; i < m.sd.n_layers; ++i) {
+    const hb_layer_desc& l = m.sl[i];
+    shape(m.sw[i].n_in, W);
+    shape(W, (size_t)l.heads * l.vdim);
+    if (l.mixer == HB_MIXER_LATENT) shape((size_t)l.heads * (l.dim + l.rot_dim), l.q_rank);
+    if (l.ff > 0) {
+      shape(2 * (size_t)l.ff, W);
+      shape(W, l.ff);
+    }
+  }
+  shape(m.sd.vocab, W);
+  return f;
+}
+
 size_t Engine::workspace_bytes_stack() const {
   const hb_stack_desc& sd = model_.sd;
   const size_t T = t_cap_, W = sd.width;
@@ -142,6 +161,7 @@ size_t Engine::workspace_bytes_stack() const {
   b += al256((size_t)cfg_.max_seqs * 4);                              // sampled
   b += al256(sample_scratch_bytes(cfg_.max_seqs, sd.vocab));
   b += 2 * al256((size_t)cfg_.max_seqs * HB_MAX_LOGPROBS * 4);
+  if (!sd.compute_f32) b += al256(stack_skinny_floats(model_) * 4);
   return b;
 }
 
@@ -193,6 +213,7 @@ int Engine::alloc_runtime_stack() {
   sample_ws_ = take(sample_scratch_bytes(cfg_.max_seqs, sd.vocab));
   lp_ids_ = (int32_t*)take((size_t)cfg_.max_seqs * HB_MAX_LOGPROBS * 4);
   lp_vals_ = (float*)take((size_t)cfg_.max_seqs * HB_MAX_LOGPROBS * 4);
+  skinny_ws_ = sd.compute_f32 ? nullptr : (float*)take(stack_skinny_floats(model_) * 4);
 
   pen_cap_ = std::min<size_t>((size_t)cfg_.max_seqs * cfg_.max_ctx, size_t(4) << 20);
   step_bytes_ = layout(t_cap_, b_cap_, pen_cap_).total;
@@ -258,7 +279,20 @@ int Engine::stack_gemm(const float* A, const bf16* A16, int lda, const void* Wt,
   const bool f32 = model_.sd.compute_f32 != 0;
   static const bool simt_only = [] { const char* e = getenv("HB_STACK_SIMT"); return e && atoi(e) != 0; }();  // A/B and bring-up
   const double flops = 2.0 * M * N * K;
-  if (!f32 && !simt_only && A16 && !bias && K % 8 == 0 && lda % 8 == 0 && ldc % 4 == 0 && K >= 64 && N >= 64) {
+  const bool tc = !f32 && !simt_only && A16 && !bias && K % 8 == 0 && lda % 8 == 0 && K >= 64 && N >= 64;
+  static const bool no_skinny = [] { const char* e = getenv("HB_STACK_SKINNY"); return e && atoi(e) == 0; }();
+  if (tc && M <= 256 && skinny_ws_ && !no_skinny) {
+    // steps of a few tokens (decoding): the weights are the MMA's M operand and stream through every SM once (stream-K over
+    // (tile, k-block) units, fp32 slabs summed in slab order: the result does not depend on who finishes first)
+    SkinnyPlan plan{};
+    CU(gemm_skinny_plan(N, K, &plan));
+    if (gemm_skinny_ws_floats(plan, M, N) <= stack_skinny_floats(model_)) {
+      SPAN(4, 2.0 * N * K + 2.0 * M * K + 4.0 * M * N, gemm_skinny(stream_, plan, A16, lda, (const bf16*)Wt, K, skinny_ws_, M, N, K));
+      SPAN(3, 8.0 * M * N, dec_sum_slabs(stream_, skinny_ws_, plan, C, ldc, M, N));
+      return HB_OK;
+    }
+  }
+  if (tc && ldc % 4 == 0) {
     GemmArgs g{A16, lda, (const bf16*)Wt, K, C, ldc, nullptr, 0, nullptr, M, N, K, EPI_F32, 0};
     SPAN(0, flops, gemm_bf16_tn(stream_, g));
     return HB_OK;

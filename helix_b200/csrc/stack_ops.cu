@@ -465,7 +465,10 @@ cudaError_t gla_decay(cudaStream_t s, float* z, long ldz, const void* bias, bool
 
 template <int DKP>
 static cudaError_t gla_launch(cudaStream_t s, const GlaArgs& a) {
-  const int cols = std::min(128, (a.Dv + 31) / 32 * 32);
+  // value columns per block: as wide as possible while the grid still covers the machine twice (the recurrence is serial
+  // in the tokens of an entry, so parallelism comes from entries x heads x column slices only)
+  int cols = std::min(128, (a.Dv + 31) / 32 * 32);
+  while (cols > 32 && (long)a.B * a.H * ((a.Dv + cols - 1) / cols) < 2 * 148) cols /= 2;
   dim3 grid(a.B, a.H, (a.Dv + cols - 1) / cols);
   gla_recurrence_kernel<DKP><<<grid, cols, (size_t)kGlaTch * 3 * DKP * 4, s>>>(a);
   return KERR();
