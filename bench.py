@@ -409,6 +409,7 @@ def bench_risepel(args):
             e = hb.Engine(hb.EngineConfig(device=0, max_seqs=sessions, max_ctx=seq + decode + 64,
                                           max_batched_tokens=args.max_batched_tokens, use_cuda_graphs=0 if args.no_graphs else 1))
             e.load_random(desc, 3)
+            e.start()  # the step-loop thread: hb_wait / hb_poll below are served by it
             prompts = [session_prompt(i, seq, desc.vocab) for i in range(sessions)]
             for _ in range(max(1, args.warmup)):
                 serve_once(e, hb, prompts[:max(1, sessions // 4)], 4)

@@ -1320,6 +1320,7 @@ int Engine::run_prefill(std::vector<Request*>& batch) {
   int32_t* seqof = (int32_t*)(h_step_ + L.seqof);
   int32_t* rows = (int32_t*)(h_step_ + L.rows);
   int n_rows = 0;
+  step_entries_.clear();
   int32_t* tok = (int32_t*)(h_step_ + L.tokens);
   int32_t* pos = (int32_t*)(h_step_ + L.positions);
   int32_t* slot = (int32_t*)(h_step_ + L.slots);
@@ -1335,6 +1336,7 @@ int Engine::run_prefill(std::vector<Request*>& batch) {
     const int end = r->prefilled + r->chunk;
     sslot[i] = r->state_slot;
     first[i] = r->prefilled;
+    step_entries_.push_back(StepEntry{t, r->prefilled, r->chunk});
     if (step_driven_)
       for (int32_t w : r->want) rows[n_rows++] = t + w;
     for (int j = r->prefilled; j < end; ++j, ++t) {
@@ -1411,6 +1413,8 @@ int Engine::run_decode(std::vector<Request*>& batch) {
     ((int32_t*)(h_step_ + L.sslot))[i] = r->state_slot;
     ((int32_t*)(h_step_ + L.first))[i] = p;
     ((int32_t*)(h_step_ + L.seqof))[i] = i;
+    if (i == 0) step_entries_.clear();
+    step_entries_.push_back(StepEntry{i, p, 1});
     tok[i] = r->out.back();
     pos[i] = p;
     slot[i] = r->pages[p / page_] * page_ + p % page_;

@@ -190,7 +190,14 @@ class Engine {
     float *x, *p1, *p2, *cq, *qabs, *ctx, *mo, *y;
     bf16 *x16, *cq16, *mo16;
     int ld1, ld2, ldcq, ldqa, ldctx, ldmo;
+    // attention of long prompt portions as dense products (bf16 mode): bf16 queries, gathered keys, scores, probabilities
+    bf16 *qabs16 = nullptr, *kbuf = nullptr, *ct = nullptr, *P = nullptr;
+    float* S = nullptr;
+    int att_qb = 0;       // tokens per query block
+    size_t att_rows = 0, att_keys = 0;  // capacity: score rows (tokens x heads) and key columns of one block
   } sk_{};
+  struct StepEntry { int t0, first, n; };  // host copy of the step's entries: first packed row, first position, tokens
+  std::vector<StepEntry> step_entries_;
   bool step_driven_ = false;             // current step comes from hb_seq_step (no sampling)
   int step_extra_rows_ = 0;
   uint8_t* ws_ = nullptr;

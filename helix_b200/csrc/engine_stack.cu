@@ -132,6 +132,32 @@ static size_t stack_skinny_floats(const Model& m) {
   return f;
 }
 
+// Dense-product attention (bf16 mode, prompt portions of >= kAttDenseMin tokens): capacity of one query block over all
+// latent layers.  Returns false when no layer qualifies (row sizes that are not 16-byte multiples).
+constexpr int kAttDenseMin = 64;
+static bool stack_att_caps(const Model& m, int* qb, size_t* rows, size_t* keys, size_t* rmax, size_t* dmax, size_t* qa16) {
+  *qb = 256; *rows = *keys = *rmax = *dmax = *qa16 = 0;
+  if (m.sd.compute_f32) return false;
+  bool any = false;
+  for (const hb_layer_desc& l : m.sl) {
+    if (l.mixer != HB_MIXER_LATENT || (l.kv_rank + l.rot_dim) % 8 || l.kv_rank % 8) continue;
+    any = true;
+    int q = 256;
+    while (q > 64 && (size_t)q * l.heads * (l.window + q) * 4 > (size_t(64) << 20)) q /= 2;  // scores of a block <= 64 MB
+    *qb = std::min(*qb, q);
+  }
+  if (!any) return false;
+  for (const hb_layer_desc& l : m.sl) {
+    if (l.mixer != HB_MIXER_LATENT || (l.kv_rank + l.rot_dim) % 8 || l.kv_rank % 8) continue;
+    *rows = std::max(*rows, (size_t)*qb * l.heads);
+    *keys = std::max(*keys, (size_t)(l.window + *qb + 7) / 8 * 8);
+    *rmax = std::max(*rmax, (size_t)l.kv_rank);
+    *dmax = std::max(*dmax, (size_t)l.kv_rank + l.rot_dim);
+    *qa16 = std::max(*qa16, (size_t)l.heads * (l.kv_rank + l.rot_dim));
+  }
+  return true;
+}
+
 size_t Engine::workspace_bytes_stack() const {
   const hb_stack_desc& sd = model_.sd;
   const size_t T = t_cap_, W = sd.width;
@@ -162,6 +188,11 @@ size_t Engine::workspace_bytes_stack() const {
   b += al256(sample_scratch_bytes(cfg_.max_seqs, sd.vocab));
   b += 2 * al256((size_t)cfg_.max_seqs * HB_MAX_LOGPROBS * 4);
   if (!sd.compute_f32) b += al256(stack_skinny_floats(model_) * 4);
+  {
+    int qb; size_t rows, keys, rmax, dmax, qa16;
+    if (stack_att_caps(model_, &qb, &rows, &keys, &rmax, &dmax, &qa16))
+      b += al256(T * qa16 * 2) + al256(keys * dmax * 2) + al256(rmax * keys * 2) + al256(rows * keys * 2) + al256(rows * keys * 4);
+  }
   return b;
 }
 
@@ -214,6 +245,17 @@ int Engine::alloc_runtime_stack() {
   lp_ids_ = (int32_t*)take((size_t)cfg_.max_seqs * HB_MAX_LOGPROBS * 4);
   lp_vals_ = (float*)take((size_t)cfg_.max_seqs * HB_MAX_LOGPROBS * 4);
   skinny_ws_ = sd.compute_f32 ? nullptr : (float*)take(stack_skinny_floats(model_) * 4);
+  {
+    int qb; size_t rows, keys, rmax, dmax, qa16;
+    if (stack_att_caps(model_, &qb, &rows, &keys, &rmax, &dmax, &qa16)) {
+      sk_.att_qb = qb; sk_.att_rows = rows; sk_.att_keys = keys;
+      sk_.qabs16 = (bf16*)take(T * qa16 * 2);
+      sk_.kbuf = (bf16*)take(keys * dmax * 2);
+      sk_.ct = (bf16*)take(rmax * keys * 2);
+      sk_.P = (bf16*)take(rows * keys * 2);
+      sk_.S = (float*)take(rows * keys * 4);
+    }
+  }
 
   pen_cap_ = std::min<size_t>((size_t)cfg_.max_seqs * cfg_.max_ctx, size_t(4) << 20);
   step_bytes_ = layout(t_cap_, b_cap_, pen_cap_).total;
@@ -356,24 +398,67 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       SPAN(3, 8.0 * T * (Q + R + Dr), latent_prep(stream_, pa));
       rc = stack_gemm(k.cq, cq16, Q, w.uq, H * (Dk + Dr), Q, k.p2, k.ld2, T);
       if (rc != HB_OK) return rc;
+      const int D = R + Dr, ldqa = H * D, ldcx = H * R;  // (token, head) rows are contiguous: row stride D / R
       {  // keys are never expanded: q_h is carried into the latent space instead (q_h^T W_uk,h), one product per head
-        GemmRtArgs g{k.p2, k.ld2, (long)(Dk + Dr), w.uk, 1, (long)R, (long)Dk * R, k.qabs, k.ldqa, (long)(R + Dr), nullptr, T, R, Dk, H, f32};
+        GemmRtArgs g{k.p2, k.ld2, (long)(Dk + Dr), w.uk, 1, (long)R, (long)Dk * R, k.qabs, ldqa, (long)D, nullptr, T, R, Dk, H, f32};
         SPAN(5, 2.0 * T * H * Dk * R, gemm_rt(stream_, g));
       }
-      SPAN(3, 8.0 * T * H * Dr, latent_q_rope(stream_, k.p2, k.ld2, k.qabs, k.ldqa, positions, T, H, Dk, Dr, R, l.rope_dims, l.rope_base));
-      LatentAttnArgs aa{};
-      aa.qabs = k.qabs; aa.ldqa = k.ldqa; aa.cache = plane; aa.f32 = f32; aa.sink = w.sink;
-      aa.page_table = pt; aa.max_pages = max_pages_per_seq_; aa.page_size = page_;
-      aa.positions = positions; aa.seq_of = seqof;
-      aa.ctx = k.ctx; aa.ldc = k.ldctx;
-      aa.T = T; aa.H = H; aa.R = R; aa.Dr = Dr; aa.window = l.window; aa.scale = l.scale;
-      SPAN(7, 2.0 * T * H * (double)std::min(l.window, cfg_.max_ctx) * (2.0 * R + Dr), latent_attn(stream_, aa));
+      SPAN(3, 8.0 * T * H * Dr, latent_q_rope(stream_, k.p2, k.ld2, k.qabs, ldqa, positions, T, H, Dk, Dr, R, l.rope_dims, l.rope_base));
+      // Long prompt portions (bf16 mode): scores and weighted latents as two tcgen05 products per block of att_qb tokens over
+      // the block's gathered keys, softmax (mask, sink) between them.  Everything else — single tokens, short portions, the
+      // exact mode — goes through the per-token kernel.  Both read the same cache rows, written by latent_prep above.
+      static const bool dense_off = [] { const char* e = getenv("HB_STACK_DENSE_ATTN"); return e && atoi(e) == 0; }();
+      const bool dense_ok = !f32 && !dense_off && k.S && D % 8 == 0 && R % 8 == 0 && (size_t)k.att_qb * H <= k.att_rows &&
+                            (size_t)l.window + k.att_qb <= k.att_keys;
+      bool any_dense = false;
+      if (dense_ok)
+        for (const StepEntry& en : step_entries_) any_dense |= en.n >= kAttDenseMin;
+      if (any_dense) SPAN(3, 6.0 * T * ldqa, to_bf16_rows(stream_, k.qabs, ldqa, k.qabs16, ldqa, T, ldqa));
+      int run0 = -1;  // start of the current run of tokens that take the per-token kernel
+      auto flush = [&](int t_end) -> int {
+        if (run0 < 0 || t_end <= run0) { run0 = -1; return HB_OK; }
+        LatentAttnArgs aa{};
+        aa.qabs = k.qabs + (size_t)run0 * ldqa; aa.ldqa = ldqa; aa.cache = plane; aa.f32 = f32; aa.sink = w.sink;
+        aa.page_table = pt; aa.max_pages = max_pages_per_seq_; aa.page_size = page_;
+        aa.positions = positions + run0; aa.seq_of = seqof + run0;
+        aa.ctx = k.ctx + (size_t)run0 * ldcx; aa.ldc = ldcx;
+        aa.T = t_end - run0; aa.H = H; aa.R = R; aa.Dr = Dr; aa.window = l.window; aa.scale = l.scale;
+        SPAN(7, 2.0 * aa.T * H * (double)std::min(l.window, cfg_.max_ctx) * (2.0 * R + Dr), latent_attn(stream_, aa));
+        run0 = -1;
+        return HB_OK;
+      };
+      for (size_t b = 0; b < step_entries_.size(); ++b) {
+        const StepEntry& en = step_entries_[b];
+        if (!(dense_ok && en.n >= kAttDenseMin)) {
+          if (run0 < 0) run0 = en.t0;
+          continue;
+        }
+        rc = flush(en.t0);
+        if (rc != HB_OK) return rc;
+        for (int q0 = 0; q0 < en.n; q0 += k.att_qb) {
+          const int nq = std::min(k.att_qb, en.n - q0);
+          const int p0 = en.first + q0;                       // position of the block's first query
+          const int k0 = std::max(0, p0 - l.window + 1);      // first key any of its queries sees
+          const int nk = p0 + nq - k0;                        // ... through the block's last token
+          const int ldk = (nk + 7) / 8 * 8;
+          const int rows = nq * H;
+          SPAN(3, 4.0 * nk * D, latent_gather(stream_, (const bf16*)plane, pt + b * max_pages_per_seq_, page_, k0, nk, R, Dr, k.kbuf, k.ct, ldk));
+          GemmArgs g1{k.qabs16 + (size_t)(en.t0 + q0) * ldqa, D, k.kbuf, D, k.S, ldk, nullptr, 0, nullptr, rows, nk, D, EPI_F32, 0};
+          SPAN(1, 2.0 * rows * nk * D, gemm_bf16_tn(stream_, g1));
+          SPAN(3, 6.0 * rows * ldk, latent_softmax(stream_, k.S, k.P, ldk, rows, H, p0, k0, nk, l.window, l.scale, (const bf16*)w.sink));
+          GemmArgs g2{k.P, ldk, k.ct, ldk, k.ctx + (size_t)(en.t0 + q0) * ldcx, R, nullptr, 0, nullptr, rows, R, ldk, EPI_F32, 0};
+          SPAN(1, 2.0 * rows * ldk * R, gemm_bf16_tn(stream_, g2));
+        }
+      }
+      rc = flush(T);
+      if (rc != HB_OK) return rc;
+      const int ldov = H * Dv;
       float* ov = k.ctx + al256((size_t)t_cap_ * k.ldctx * 4) / 4;  // per-head values out of the weighted latent
       {
-        GemmRtArgs g{k.ctx, k.ldctx, (long)R, w.uv, (long)R, 1, (long)Dv * R, ov, k.ldctx, (long)Dv, nullptr, T, Dv, R, H, f32};
+        GemmRtArgs g{k.ctx, ldcx, (long)R, w.uv, (long)R, 1, (long)Dv * R, ov, ldov, (long)Dv, nullptr, T, Dv, R, H, f32};
         SPAN(5, 2.0 * T * H * Dv * R, gemm_rt(stream_, g));
       }
-      SPAN(3, 12.0 * T * H * Dv, sigmoid_gate(stream_, ov, k.ldctx, k.p1 + w.off_g, k.ld1, k.mo, mo16, T, H * Dv));
+      SPAN(3, 12.0 * T * H * Dv, sigmoid_gate(stream_, ov, ldov, k.p1 + w.off_g, k.ld1, k.mo, mo16, T, H * Dv));
     }
     rc = stack_gemm(k.mo, mo16, H * Dv, w.wo, W, H * Dv, k.y, W, T);
     if (rc != HB_OK) return rc;

@@ -322,6 +322,17 @@ struct LatentAttnArgs {
   float scale;
 };
 cudaError_t latent_attn(cudaStream_t s, const LatentAttnArgs& a);
+// The same attention as three dense products for a block of consecutive tokens of ONE sequence (long prompt portions in the
+// bf16 mode; the two products run on the tcgen05 GEMM):
+//   latent_gather:  kbuf[jj] = cache row of position k0 + jj (jj < nk), ct[r][jj] = its latent entry r (columns nk..ldk zero)
+//   S = qabs16 . kbuf^T  (rows (token, head))        -> latent_softmax: masked, sink-normalised probabilities as bf16
+//   ctx = P . ct^T
+cudaError_t latent_gather(cudaStream_t s, const bf16* cache, const int32_t* page_table_row, int page_size, int k0, int nk, int R,
+                          int Dr, bf16* kbuf, bf16* ct, int ldk);
+// P[(tq, h), jj] = softmax over the keys position q0 + tq sees (0 <= q0 + tq - (k0 + jj) < window) with sink_h in the
+// denominator; S and P have row stride ld, columns >= nk of P are written as zero
+cudaError_t latent_softmax(cudaStream_t s, const float* S, bf16* P, int ld, int rows, int H, int q0, int k0, int nk, int window,
+                           float scale, const bf16* sink);
 // out = o * sigmoid(g)
 cudaError_t sigmoid_gate(cudaStream_t s, const float* o, long ldo, const float* g, long ldg, float* out, bf16* out_b16, int T, int N);
 // f32 -> bf16 copy of a [T, N] block (row strides lds / ldd)

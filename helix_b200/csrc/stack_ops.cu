@@ -328,14 +328,41 @@ __global__ void latent_q_rope_kernel(const float* __restrict__ q, long ldq, floa
   }
 }
 
-// One block per (token, head).  dynamic smem: q [R+Dr] + scores [window] + 32.
+// One block per (token, head), kLatThreads threads.  dynamic smem: q [R+Dr] + scores [window] + partial sums [threads] + 32.
+// Scores: one warp per key (16-byte loads of bf16 rows when the row length allows).  Weighted sum: thread (g, r) adds the
+// keys jj = g mod G of latent entry r, groups are then summed in group order — fixed per (R, threads), independent of the batch.
+constexpr int kLatThreads = 512;
+__device__ __forceinline__ float dot_row(const float* __restrict__ qs, const float* __restrict__ row, int D, int l) {
+  float s = 0.f;
+  for (int i = l; i < D; i += 32) s = fmaf(qs[i], row[i], s);
+  return s;
+}
+__device__ __forceinline__ float dot_row(const float* __restrict__ qs, const bf16* __restrict__ row, int D, int l) {
+  float s = 0.f;
+  if ((D & 7) == 0) {  // rows start on 16-byte boundaries
+    for (int i = l * 8; i < D; i += 256) {
+      const uint4 u = *reinterpret_cast<const uint4*>(row + i);
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(p2[e]);
+        s = fmaf(qs[i + 2 * e], f.x, s);
+        s = fmaf(qs[i + 2 * e + 1], f.y, s);
+      }
+    }
+  } else {
+    for (int i = l; i < D; i += 32) s = fmaf(qs[i], __bfloat162float(row[i]), s);
+  }
+  return s;
+}
 template <typename WT, typename CT>
-__global__ void __launch_bounds__(128) latent_attn_kernel(LatentAttnArgs a) {
+__global__ void __launch_bounds__(kLatThreads) latent_attn_kernel(LatentAttnArgs a) {
   extern __shared__ float sm[];
   const int D = a.R + a.Dr;
   float* qs = sm;
-  float* sc = sm + D;
-  float* red = sc + a.window;
+  float* sc = sm + (D + 3) / 4 * 4;
+  float* part = sc + a.window;
+  float* red = part + blockDim.x;
   const int t = blockIdx.x, h = blockIdx.y;
   const int pos = a.positions[t];
   const int n = min(pos + 1, a.window), j0 = pos - n + 1;  // keys j0 .. pos
@@ -347,9 +374,7 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(LatentAttnArgs a) {
   for (int jj = w; jj < n; jj += nw) {
     const int j = j0 + jj;
     const CT* row = cache + ((size_t)pt[j / a.page_size] * a.page_size + j % a.page_size) * D;
-    float s = 0.f;
-    for (int i = l; i < D; i += 32) s = fmaf(qs[i], ldf<CT>(row, i), s);
-    s = warp_sum(s);
+    const float s = warp_sum(dot_row(qs, row, D, l));
     if (l == 0) sc[jj] = s * a.scale;
   }
   __syncthreads();
@@ -365,20 +390,89 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(LatentAttnArgs a) {
   }
   sum = block_sum(sum, red) + expf(sink - m);  // block_sum's barriers also publish sc[]
   const float inv = 1.f / sum;
-  for (int r = threadIdx.x; r < a.R; r += blockDim.x) {
+  const int Rp = (a.R + 31) / 32 * 32;
+  const int G = max(1, (int)blockDim.x / Rp);
+  for (int r0 = 0; r0 < a.R; r0 += blockDim.x) {  // one pass unless the latent is wider than the block
+    const int g = (G > 1) ? threadIdx.x / Rp : 0, r = r0 + ((G > 1) ? threadIdx.x % Rp : threadIdx.x);
     float acc = 0.f;
-    for (int jj = 0; jj < n; ++jj) {
-      const int j = j0 + jj;
-      const CT* row = cache + ((size_t)pt[j / a.page_size] * a.page_size + j % a.page_size) * D;
-      acc = fmaf(sc[jj], ldf<CT>(row, r), acc);
+    if (g < G && r < a.R) {
+      for (int jj = g; jj < n; jj += G) {
+        const int j = j0 + jj;
+        const CT* row = cache + ((size_t)pt[j / a.page_size] * a.page_size + j % a.page_size) * D;
+        acc = fmaf(sc[jj], ldf<CT>(row, r), acc);
+      }
     }
-    a.ctx[(size_t)t * a.ldc + (size_t)h * a.R + r] = acc * inv;
+    if (G > 1) {
+      __syncthreads();
+      part[threadIdx.x] = acc;
+      __syncthreads();
+      if (threadIdx.x < a.R) {
+        float tot = 0.f;
+        for (int gg = 0; gg < G; ++gg) tot += part[gg * Rp + threadIdx.x];
+        a.ctx[(size_t)t * a.ldc + (size_t)h * a.R + threadIdx.x] = tot * inv;
+      }
+    } else if (r < a.R) {
+      a.ctx[(size_t)t * a.ldc + (size_t)h * a.R + r] = acc * inv;
+    }
   }
+}
+
+// block per key row jj
+__global__ void __launch_bounds__(128) latent_gather_kernel(const bf16* __restrict__ cache, const int32_t* __restrict__ pt, int page_size,
+                                                            int k0, int nk, int R, int Dr, bf16* __restrict__ kbuf,
+                                                            bf16* __restrict__ ct, int ldk) {
+  const int jj = blockIdx.x, D = R + Dr;
+  if (jj >= nk) {  // padding columns of ct must be exact zeros: they meet the zero tail of P in the second product
+    for (int r = threadIdx.x; r < R; r += blockDim.x) ct[(size_t)r * ldk + jj] = __float2bfloat16(0.f);
+    return;
+  }
+  const int pos = k0 + jj;
+  const bf16* row = cache + ((size_t)pt[pos / page_size] * page_size + pos % page_size) * D;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const bf16 v = row[i];
+    kbuf[(size_t)jj * D + i] = v;
+    if (i < R) ct[(size_t)i * ldk + jj] = v;
+  }
+}
+
+// one warp per row (token, head)
+__global__ void __launch_bounds__(128) latent_softmax_kernel(const float* __restrict__ S, bf16* __restrict__ P, int ld, int rows, int H,
+                                                             int q0, int k0, int nk, int window, float scale,
+                                                             const bf16* __restrict__ sink) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int l = threadIdx.x & 31;
+  const int pos = q0 + row / H, h = row % H;
+  const int lo = max(pos - window + 1, k0) - k0, hi = min(pos, k0 + nk - 1) - k0;  // visible columns [lo, hi]
+  const float* s = S + (size_t)row * ld;
+  bf16* p = P + (size_t)row * ld;
+  const float snk = __bfloat162float(sink[h]);
+  float m = snk;
+  for (int j = lo + l; j <= hi; j += 32) m = fmaxf(m, s[j] * scale);
+  m = warp_max(m);
+  float sum = 0.f;
+  for (int j = lo + l; j <= hi; j += 32) sum += expf(s[j] * scale - m);
+  sum = warp_sum(sum) + expf(snk - m);
+  const float inv = 1.f / sum;
+  for (int j = l; j < ld; j += 32) p[j] = __float2bfloat16((j >= lo && j <= hi) ? expf(s[j] * scale - m) * inv : 0.f);
 }
 
 }  // namespace
 
 #define KERR() cudaGetLastError()
+
+cudaError_t latent_gather(cudaStream_t s, const bf16* cache, const int32_t* pt, int page_size, int k0, int nk, int R, int Dr, bf16* kbuf,
+                          bf16* ct, int ldk) {
+  if (nk <= 0 || ldk < nk) return cudaErrorInvalidValue;
+  latent_gather_kernel<<<ldk, 128, 0, s>>>(cache, pt, page_size, k0, nk, R, Dr, kbuf, ct, ldk);
+  return KERR();
+}
+cudaError_t latent_softmax(cudaStream_t s, const float* S, bf16* P, int ld, int rows, int H, int q0, int k0, int nk, int window,
+                           float scale, const bf16* sink) {
+  if (rows <= 0) return cudaSuccess;
+  latent_softmax_kernel<<<(rows + 3) / 4, 128, 0, s>>>(S, P, ld, rows, H, q0, k0, nk, window, scale, sink);
+  return KERR();
+}
 
 cudaError_t gemm_rt(cudaStream_t s, const GemmRtArgs& a) {
   if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.batch <= 0) return cudaErrorInvalidValue;
@@ -508,7 +602,7 @@ cudaError_t latent_q_rope(cudaStream_t s, const float* q, long ldq, float* qabs,
 
 cudaError_t latent_attn(cudaStream_t s, const LatentAttnArgs& a) {
   if (a.T <= 0) return cudaSuccess;
-  const size_t smem = (size_t)(a.R + a.Dr + a.window + 32) * 4;
+  const size_t smem = (size_t)((a.R + a.Dr + 3) / 4 * 4 + a.window + kLatThreads + 32) * 4;
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
   if (smem > 48 * 1024) {
     static bool done[2] = {false, false};
@@ -520,8 +614,8 @@ cudaError_t latent_attn(cudaStream_t s, const LatentAttnArgs& a) {
     }
   }
   dim3 grid(a.T, a.H);
-  if (a.f32) latent_attn_kernel<float, float><<<grid, 128, smem, s>>>(a);
-  else latent_attn_kernel<bf16, bf16><<<grid, 128, smem, s>>>(a);
+  if (a.f32) latent_attn_kernel<float, float><<<grid, kLatThreads, smem, s>>>(a);
+  else latent_attn_kernel<bf16, bf16><<<grid, kLatThreads, smem, s>>>(a);
   return KERR();
 }
 
