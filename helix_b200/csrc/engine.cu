@@ -1429,17 +1429,16 @@ int Engine::run_decode(std::vector<Request*>& batch) {
   attn_bytes_ = 0;
   for (Request* r : batch) attn_bytes_ += (double)(r->kv_len + 1) * 2.0 * d.kv_heads * d.head_dim * 2.0;
   CU(cudaEventRecord(fwd_a_, stream_));
-  if (is_stack()) {  // one forward for every kind of step: a decode step is B one-token entries
-    int rc = forward_stack(B, B, L, nullptr, 0, nullptr, true);
-    if (rc != HB_OK) return rc;
-  } else if (cfg_.use_cuda_graphs && !profile_) {
+  // layer-list decoders have one forward for every kind of step: a decode step is B one-token entries
+  auto fwd = [&]() { return is_stack() ? forward_stack(B, B, L, nullptr, 0, nullptr, true) : forward_llama(B, B, false, 1, L, false); };
+  if (cfg_.use_cuda_graphs && !profile_) {
     const int gkey = B | (step_flags_ << 20);  // filter / penalty / log-probability passes are different kernel sequences
     auto it = graphs_.find(gkey);
     if (it == graphs_.end()) {
       cudaGraph_t graph = nullptr;
       const uint64_t l0 = launches_.load();
       CU(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
-      int rc = forward_llama(B, B, false, 1, L, false);
+      int rc = fwd();
       cudaError_t ce = cudaStreamEndCapture(stream_, &graph);
       graph_kernels_[gkey] = launches_.load() - l0;
       launches_.store(l0);  // captured, not executed
@@ -1454,7 +1453,7 @@ int Engine::run_decode(std::vector<Request*>& batch) {
     graph_launches_++;
     launches_.fetch_add(graph_kernels_[gkey]);
   } else {
-    int rc = forward_llama(B, B, false, 1, L, false);
+    int rc = fwd();
     if (rc != HB_OK) return rc;
   }
   CU(cudaEventRecord(fwd_b_, stream_));

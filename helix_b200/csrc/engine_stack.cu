@@ -199,7 +199,22 @@ size_t Engine::workspace_bytes_stack() const {
 int Engine::alloc_runtime_stack() {
   const hb_stack_desc& sd = model_.sd;
   cfg_.enable_prefix_cache = 0;  // a page of latent rows does not carry the recurrent layers' state of its prefix
-  cfg_.use_cuda_graphs = 0;
+  CU(stack_ops_init());
+  if (!sd.compute_f32) {  // stream-K plans allocate on first use of a shape: make them now, not inside a graph capture
+    SmLimitScope sm_scope(cfg_.sm_budget);
+    SkinnyPlan pl{};
+    for (int i = 0; i < sd.n_layers; ++i) {
+      const hb_layer_desc& l = model_.sl[i];
+      CU(gemm_skinny_plan(model_.sw[i].n_in, sd.width, &pl));
+      CU(gemm_skinny_plan(sd.width, l.heads * l.vdim, &pl));
+      if (l.mixer == HB_MIXER_LATENT) CU(gemm_skinny_plan(l.heads * (l.dim + l.rot_dim), l.q_rank, &pl));
+      if (l.ff > 0) {
+        CU(gemm_skinny_plan(2 * l.ff, sd.width, &pl));
+        CU(gemm_skinny_plan(sd.width, l.ff, &pl));
+      }
+    }
+    CU(gemm_skinny_plan(sd.vocab, sd.width, &pl));
+  }
   t_cap_ = cfg_.max_batched_tokens;
   b_cap_ = cfg_.max_seqs;
   max_pages_per_seq_ = (cfg_.max_ctx + page_ - 1) / page_;

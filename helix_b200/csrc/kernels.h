@@ -246,6 +246,7 @@ cudaError_t dec_swiglu(cudaStream_t s, const float* ws, const SkinnyPlan& p, bf1
 // C[z][m, n] = sum_k A[z][m, k] * W[z](n, k) (+ bias[n]): CUDA-core fp32 FMA GEMM for shapes or precisions the tcgen05
 // GEMMs do not take (true 32-bit mode, strides that are not 16-byte multiples, per-head batched products).
 // W(n, k) = W[z * w_bs + n * w_sn + k * w_sk]; k runs sequentially inside a thread, so a row's result does not depend on M.
+cudaError_t stack_ops_init();  // opt-in shared-memory attributes of the kernels below (once, outside any graph capture)
 struct GemmRtArgs {
   const float* A; long lda; long a_bs;
   const void* W; long w_sn, w_sk, w_bs;

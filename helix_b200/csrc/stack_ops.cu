@@ -190,38 +190,65 @@ __global__ void gla_decay_kernel(float* __restrict__ z, long ldz, const WT* __re
 
 // One block per (entry, head, slice of value columns); thread j owns column j of the state (DKP >= Dk fp32 registers).
 // Tokens are staged through shared memory TCH at a time: q, k, decay of the head are the same for every thread.
-constexpr int kGlaTch = 8;
+constexpr int kGlaTch = 16;
+__device__ __forceinline__ void cp_async4(float* smem_dst, const float* gsrc) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <int DKP>
 __global__ void __launch_bounds__(128) gla_recurrence_kernel(GlaArgs a) {
-  extern __shared__ float sm[];  // [kGlaTch][3][DKP]
+  extern __shared__ float sm[];  // 2 stages x [kGlaTch][3 * DKP + blockDim.x]
   const int b = blockIdx.x, h = blockIdx.y;
-  const int j = blockIdx.z * blockDim.x + threadIdx.x;
+  const int c0 = blockIdx.z * blockDim.x;
+  const int j = c0 + threadIdx.x;
   const bool live = j < a.Dv;
   const int t0 = a.cu[b], t1 = a.cu[b + 1];
   const int Dk = a.Dk;
+  const int per_tok = 3 * DKP + blockDim.x, stage_floats = kGlaTch * per_tok;
   float* st = a.state + (size_t)a.slots[b] * a.slot_stride + (size_t)h * Dk * a.Dv;
   float S[DKP];
   const bool fresh = a.first_pos[b] == 0;
 #pragma unroll
   for (int i = 0; i < DKP; ++i) S[i] = (!fresh && live && i < Dk) ? st[(size_t)i * a.Dv + j] : 0.f;
-  for (int tc = t0; tc < t1; tc += kGlaTch) {
+  // padded key channels read zeros: clear them once, the copies below only touch i < Dk
+  for (int e = threadIdx.x; e < 2 * stage_floats; e += blockDim.x) sm[e] = 0.f;
+  __syncthreads();
+  auto issue = [&](int tc, int stage) {
     const int nt = min(kGlaTch, t1 - tc);
-    __syncthreads();
-    for (int e = threadIdx.x; e < nt * DKP; e += blockDim.x) {
-      const int tt = e / DKP, i = e % DKP;
+    float* base = sm + stage * stage_floats;
+    for (int e = threadIdx.x; e < nt * Dk; e += blockDim.x) {
+      const int tt = e / Dk, i = e % Dk;
       const size_t row = (size_t)(tc + tt);
-      const bool in = i < Dk;
-      sm[(tt * 3 + 0) * DKP + i] = in ? a.q[row * a.ld + h * Dk + i] : 0.f;
-      sm[(tt * 3 + 1) * DKP + i] = in ? a.k[row * a.ld + h * Dk + i] : 0.f;
-      sm[(tt * 3 + 2) * DKP + i] = in ? a.decay[row * a.ldd + h * Dk + i] : 0.f;
+      float* dst = base + tt * per_tok;
+      cp_async4(dst + i, a.q + row * a.ld + h * Dk + i);
+      cp_async4(dst + DKP + i, a.k + row * a.ld + h * Dk + i);
+      cp_async4(dst + 2 * DKP + i, a.decay + row * a.ldd + h * Dk + i);
+    }
+    if (live)
+      for (int tt = 0; tt < nt; ++tt) cp_async4(base + tt * per_tok + 3 * DKP + threadIdx.x, a.v + (size_t)(tc + tt) * a.ld + (size_t)h * a.Dv + j);
+    cp_async_commit();
+  };
+  if (t0 < t1) issue(t0, 0);
+  int stage = 0;
+  for (int tc = t0; tc < t1; tc += kGlaTch, stage ^= 1) {
+    const int nt = min(kGlaTch, t1 - tc);
+    if (tc + kGlaTch < t1) {
+      issue(tc + kGlaTch, stage ^ 1);  // next tokens travel while these are consumed
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
     __syncthreads();
+    const float* base = sm + stage * stage_floats;
     for (int tt = 0; tt < nt; ++tt) {
-      const size_t row = (size_t)(tc + tt);
-      const float vj = live ? a.v[row * a.ld + (size_t)h * a.Dv + j] : 0.f;
-      const float4* q4 = reinterpret_cast<const float4*>(sm + (tt * 3 + 0) * DKP);
-      const float4* k4 = reinterpret_cast<const float4*>(sm + (tt * 3 + 1) * DKP);
-      const float4* d4 = reinterpret_cast<const float4*>(sm + (tt * 3 + 2) * DKP);
+      const float* tk = base + tt * per_tok;
+      const float vj = tk[3 * DKP + threadIdx.x];
+      const float4* q4 = reinterpret_cast<const float4*>(tk);
+      const float4* k4 = reinterpret_cast<const float4*>(tk + DKP);
+      const float4* d4 = reinterpret_cast<const float4*>(tk + 2 * DKP);
       float o = 0.f;
 #pragma unroll
       for (int i = 0; i < DKP / 4; ++i) {
@@ -231,8 +258,9 @@ __global__ void __launch_bounds__(128) gla_recurrence_kernel(GlaArgs a) {
         S[4 * i + 2] = fmaf(d.z, S[4 * i + 2], k.z * vj); o = fmaf(S[4 * i + 2], q.z, o);
         S[4 * i + 3] = fmaf(d.w, S[4 * i + 3], k.w * vj); o = fmaf(S[4 * i + 3], q.w, o);
       }
-      if (live) a.out[row * a.ldo + (size_t)h * a.Dv + j] = o * a.q_scale;
+      if (live) a.out[(size_t)(tc + tt) * a.ldo + (size_t)h * a.Dv + j] = o * a.q_scale;
     }
+    __syncthreads();  // the stage is rewritten by the copies issued in the next iteration
   }
   if (live) {
 #pragma unroll
@@ -331,7 +359,7 @@ __global__ void latent_q_rope_kernel(const float* __restrict__ q, long ldq, floa
 // One block per (token, head), kLatThreads threads.  dynamic smem: q [R+Dr] + scores [window] + partial sums [threads] + 32.
 // Scores: one warp per key (16-byte loads of bf16 rows when the row length allows).  Weighted sum: thread (g, r) adds the
 // keys jj = g mod G of latent entry r, groups are then summed in group order — fixed per (R, threads), independent of the batch.
-constexpr int kLatThreads = 512;
+constexpr int kLatThreads = 1024;
 __device__ __forceinline__ float dot_row(const float* __restrict__ qs, const float* __restrict__ row, int D, int l) {
   float s = 0.f;
   for (int i = l; i < D; i += 32) s = fmaf(qs[i], row[i], s);
@@ -363,17 +391,21 @@ __global__ void __launch_bounds__(kLatThreads) latent_attn_kernel(LatentAttnArgs
   float* sc = sm + (D + 3) / 4 * 4;
   float* part = sc + a.window;
   float* red = part + blockDim.x;
+  int* rowoff = reinterpret_cast<int*>(red + 32);  // cache row of every visible key (page lookup done once)
   const int t = blockIdx.x, h = blockIdx.y;
   const int pos = a.positions[t];
   const int n = min(pos + 1, a.window), j0 = pos - n + 1;  // keys j0 .. pos
   const int32_t* pt = a.page_table + (size_t)a.seq_of[t] * a.max_pages;
   const CT* cache = (const CT*)a.cache;
   for (int i = threadIdx.x; i < D; i += blockDim.x) qs[i] = a.qabs[(size_t)t * a.ldqa + (size_t)h * D + i];
+  for (int jj = threadIdx.x; jj < n; jj += blockDim.x) {
+    const int j = j0 + jj;
+    rowoff[jj] = pt[j / a.page_size] * a.page_size + j % a.page_size;
+  }
   __syncthreads();
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
   for (int jj = w; jj < n; jj += nw) {
-    const int j = j0 + jj;
-    const CT* row = cache + ((size_t)pt[j / a.page_size] * a.page_size + j % a.page_size) * D;
+    const CT* row = cache + (size_t)rowoff[jj] * D;
     const float s = warp_sum(dot_row(qs, row, D, l));
     if (l == 0) sc[jj] = s * a.scale;
   }
@@ -396,11 +428,17 @@ __global__ void __launch_bounds__(kLatThreads) latent_attn_kernel(LatentAttnArgs
     const int g = (G > 1) ? threadIdx.x / Rp : 0, r = r0 + ((G > 1) ? threadIdx.x % Rp : threadIdx.x);
     float acc = 0.f;
     if (g < G && r < a.R) {
-      for (int jj = g; jj < n; jj += G) {
-        const int j = j0 + jj;
-        const CT* row = cache + ((size_t)pt[j / a.page_size] * a.page_size + j % a.page_size) * D;
-        acc = fmaf(sc[jj], ldf<CT>(row, r), acc);
+      const CT* col = cache + r;
+      int jj = g;
+      for (; jj + 3 * G < n; jj += 4 * G) {  // four independent loads in flight; the sum keeps key order
+        const float c0 = ldf<CT>(col, (size_t)rowoff[jj] * D), c1 = ldf<CT>(col, (size_t)rowoff[jj + G] * D);
+        const float c2 = ldf<CT>(col, (size_t)rowoff[jj + 2 * G] * D), c3 = ldf<CT>(col, (size_t)rowoff[jj + 3 * G] * D);
+        acc = fmaf(sc[jj], c0, acc);
+        acc = fmaf(sc[jj + G], c1, acc);
+        acc = fmaf(sc[jj + 2 * G], c2, acc);
+        acc = fmaf(sc[jj + 3 * G], c3, acc);
       }
+      for (; jj < n; jj += G) acc = fmaf(sc[jj], ldf<CT>(col, (size_t)rowoff[jj] * D), acc);
     }
     if (G > 1) {
       __syncthreads();
@@ -474,6 +512,23 @@ cudaError_t latent_softmax(cudaStream_t s, const float* S, bf16* P, int ld, int 
   return KERR();
 }
 
+// opt-in shared-memory sizes of every kernel here; called once per process before the first launch (never inside a capture)
+cudaError_t stack_ops_init() {
+  cudaError_t e;
+  const int big = 200 * 1024;
+#define HB_SMEM(k, n) if ((e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, n)) != cudaSuccess) return e
+  HB_SMEM(postnorm_kernel<float>, big);
+  HB_SMEM(postnorm_kernel<bf16>, big);
+  HB_SMEM((latent_attn_kernel<float, float>), big);
+  HB_SMEM((latent_attn_kernel<bf16, bf16>), big);
+  HB_SMEM(gla_recurrence_kernel<16>, 64 * 1024);
+  HB_SMEM(gla_recurrence_kernel<32>, 64 * 1024);
+  HB_SMEM(gla_recurrence_kernel<64>, 64 * 1024);
+  HB_SMEM(gla_recurrence_kernel<128>, 64 * 1024);
+#undef HB_SMEM
+  return cudaSuccess;
+}
+
 cudaError_t gemm_rt(cudaStream_t s, const GemmRtArgs& a) {
   if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.batch <= 0) return cudaErrorInvalidValue;
   dim3 grid((a.N + GT - 1) / GT, (a.M + GT - 1) / GT, a.batch);
@@ -497,16 +552,7 @@ static cudaError_t postnorm_launch(cudaStream_t s, const float* x, const int32_t
                                    const void* w, bool f32, float alpha, float off, float eps, float* out, bf16* outb, int rows, int W) {
   if (rows <= 0) return cudaSuccess;
   const size_t smem = (size_t)(W + 32) * 4;
-  if (smem > 48 * 1024) {
-    static bool done[2] = {false, false};
-    if (!done[f32]) {
-      cudaError_t e = f32 ? cudaFuncSetAttribute(postnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
-                          : cudaFuncSetAttribute(postnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-      if (e != cudaSuccess) return e;
-      done[f32] = true;
-    }
-    if (smem > 200 * 1024) return cudaErrorInvalidValue;
-  }
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;
   if (f32)
     postnorm_kernel<float><<<rows, 256, smem, s>>>(x, idx, y, ldy, (const float*)bias, (const float*)w, alpha, off, eps, out, outb, W);
   else
@@ -564,7 +610,8 @@ static cudaError_t gla_launch(cudaStream_t s, const GlaArgs& a) {
   int cols = std::min(128, (a.Dv + 31) / 32 * 32);
   while (cols > 32 && (long)a.B * a.H * ((a.Dv + cols - 1) / cols) < 2 * 148) cols /= 2;
   dim3 grid(a.B, a.H, (a.Dv + cols - 1) / cols);
-  gla_recurrence_kernel<DKP><<<grid, cols, (size_t)kGlaTch * 3 * DKP * 4, s>>>(a);
+  const size_t smem = (size_t)2 * kGlaTch * (3 * DKP + cols) * 4;  // <= 2 * 16 * 512 * 4 = 64 KB
+  gla_recurrence_kernel<DKP><<<grid, cols, smem, s>>>(a);
   return KERR();
 }
 cudaError_t gla_recurrence(cudaStream_t s, const GlaArgs& a) {
@@ -602,17 +649,8 @@ cudaError_t latent_q_rope(cudaStream_t s, const float* q, long ldq, float* qabs,
 
 cudaError_t latent_attn(cudaStream_t s, const LatentAttnArgs& a) {
   if (a.T <= 0) return cudaSuccess;
-  const size_t smem = (size_t)((a.R + a.Dr + 3) / 4 * 4 + a.window + kLatThreads + 32) * 4;
+  const size_t smem = (size_t)((a.R + a.Dr + 3) / 4 * 4 + 2 * a.window + kLatThreads + 32) * 4;
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
-  if (smem > 48 * 1024) {
-    static bool done[2] = {false, false};
-    if (!done[a.f32]) {
-      cudaError_t e = a.f32 ? cudaFuncSetAttribute(latent_attn_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
-                            : cudaFuncSetAttribute(latent_attn_kernel<bf16, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-      if (e != cudaSuccess) return e;
-      done[a.f32] = true;
-    }
-  }
   dim3 grid(a.T, a.H);
   if (a.f32) latent_attn_kernel<float, float><<<grid, kLatThreads, smem, s>>>(a);
   else latent_attn_kernel<bf16, bf16><<<grid, kLatThreads, smem, s>>>(a);

@@ -263,6 +263,12 @@ def test_continuous_batching_and_mixed_steps_match_solo_runs():
         _, mixed = e.generate(prompts, sp)  # prompts cut into 64-token portions beside the running sequences' tokens
         assert e.stats()["steps_mixed"] > 0
         assert mixed == solo
+    with make_engine(cfg, sd, 1, max_seqs=4, ctx=256, use_cuda_graphs=1) as e:
+        _, graphed = e.generate(prompts, sp)  # decode steps replayed from CUDA graphs (one per batch size)
+        assert e.stats()["graph_launches"] > 0
+        assert graphed == solo
+    with make_engine(cfg, sd, 0, max_seqs=4, ctx=256) as e0, make_engine(cfg, sd, 0, max_seqs=4, ctx=256, use_cuda_graphs=1) as e1:
+        assert e0.generate(prompts, sp)[1] == e1.generate(prompts, sp)[1]  # serving mode: same kernels, same ids
 
 
 def test_random_weights_and_bad_descriptions():
