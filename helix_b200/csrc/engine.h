@@ -191,6 +191,7 @@ class Engine {
     bf16 *x16, *cq16, *mo16;
     int ld1, ld2, ldcq, ldqa, ldctx, ldmo;
     // attention of long prompt portions as dense products (bf16 mode): bf16 queries, gathered keys, scores, probabilities
+    bf16 *q16 = nullptr, *ctx16 = nullptr;  // bf16 copies of the per-head queries / weighted latents (per-head tcgen05 products)
     bf16 *qabs16 = nullptr, *kbuf = nullptr, *ct = nullptr, *P = nullptr;
     float* S = nullptr;
     int att_qb = 0;       // tokens per query block

@@ -187,7 +187,7 @@ size_t Engine::workspace_bytes_stack() const {
   b += al256((size_t)cfg_.max_seqs * 4);                              // sampled
   b += al256(sample_scratch_bytes(cfg_.max_seqs, sd.vocab));
   b += 2 * al256((size_t)cfg_.max_seqs * HB_MAX_LOGPROBS * 4);
-  if (!sd.compute_f32) b += al256(stack_skinny_floats(model_) * 4);
+  if (!sd.compute_f32) b += al256(stack_skinny_floats(model_) * 4) + al256(T * (size_t)up8(n2) * 2) + al256(T * (size_t)up8(cx) * 2);
   {
     int qb; size_t rows, keys, rmax, dmax, qa16;
     if (stack_att_caps(model_, &qb, &rows, &keys, &rmax, &dmax, &qa16))
@@ -260,6 +260,16 @@ int Engine::alloc_runtime_stack() {
   lp_ids_ = (int32_t*)take((size_t)cfg_.max_seqs * HB_MAX_LOGPROBS * 4);
   lp_vals_ = (float*)take((size_t)cfg_.max_seqs * HB_MAX_LOGPROBS * 4);
   skinny_ws_ = sd.compute_f32 ? nullptr : (float*)take(stack_skinny_floats(model_) * 4);
+  if (!sd.compute_f32) {
+    sk_.q16 = (bf16*)take(T * (size_t)sk_.ld2 * 2);
+    sk_.ctx16 = (bf16*)take(T * (size_t)sk_.ldctx * 2);
+    for (int i = 0; i < sd.n_layers; ++i) {  // per-head transposed key up-projections (arena slots without a checkpoint tensor)
+      const hb_layer_desc& l = model_.sl[i];
+      if (l.mixer == HB_MIXER_LATENT && model_.sw[i].ukT)
+        CU(transpose_heads_bf16(stream_, (const bf16*)model_.sw[i].uk, (bf16*)model_.sw[i].ukT, l.heads, l.dim, l.kv_rank));
+    }
+    CU(cudaStreamSynchronize(stream_));
+  }
   {
     int qb; size_t rows, keys, rmax, dmax, qa16;
     if (stack_att_caps(model_, &qb, &rows, &keys, &rmax, &dmax, &qa16)) {
@@ -414,7 +424,19 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       rc = stack_gemm(k.cq, cq16, Q, w.uq, H * (Dk + Dr), Q, k.p2, k.ld2, T);
       if (rc != HB_OK) return rc;
       const int D = R + Dr, ldqa = H * D, ldcx = H * R;  // (token, head) rows are contiguous: row stride D / R
-      {  // keys are never expanded: q_h is carried into the latent space instead (q_h^T W_uk,h), one product per head
+      // keys are never expanded: q_h is carried into the latent space instead (q_h^T W_uk,h), one product per head —
+      // on the tensor cores for steps of many tokens (bf16 copy of q, W_uk transposed per head at load), else one batched
+      // CUDA-core launch
+      const bool head_tc = !f32 && T > 256 && w.ukT && k.q16 && (Dk + Dr) % 8 == 0 && Dk % 8 == 0 && Dk >= 64 && R % 8 == 0 &&
+                           R >= 64 && D % 4 == 0 && Dv % 4 == 0 && Dv >= 64 && !getenv("HB_STACK_SIMT");
+      if (head_tc) {
+        SPAN(3, 6.0 * T * H * (Dk + Dr), to_bf16_rows(stream_, k.p2, k.ld2, k.q16, k.ld2, T, H * (Dk + Dr)));
+        for (int h = 0; h < H; ++h) {
+          GemmArgs g{k.q16 + (size_t)h * (Dk + Dr), k.ld2, (const bf16*)w.ukT + (size_t)h * R * Dk, Dk, k.qabs + (size_t)h * D, ldqa,
+                     nullptr, 0, nullptr, T, R, Dk, EPI_F32, 0};
+          SPAN(0, 2.0 * T * R * Dk, gemm_bf16_tn(stream_, g));
+        }
+      } else {
         GemmRtArgs g{k.p2, k.ld2, (long)(Dk + Dr), w.uk, 1, (long)R, (long)Dk * R, k.qabs, ldqa, (long)D, nullptr, T, R, Dk, H, f32};
         SPAN(5, 2.0 * T * H * Dk * R, gemm_rt(stream_, g));
       }
@@ -469,7 +491,14 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       if (rc != HB_OK) return rc;
       const int ldov = H * Dv;
       float* ov = k.ctx + al256((size_t)t_cap_ * k.ldctx * 4) / 4;  // per-head values out of the weighted latent
-      {
+      if (head_tc) {
+        SPAN(3, 6.0 * T * ldcx, to_bf16_rows(stream_, k.ctx, ldcx, k.ctx16, ldcx, T, ldcx));
+        for (int h = 0; h < H; ++h) {
+          GemmArgs g{k.ctx16 + (size_t)h * R, ldcx, (const bf16*)w.uv + (size_t)h * Dv * R, R, ov + (size_t)h * Dv, ldov,
+                     nullptr, 0, nullptr, T, Dv, R, EPI_F32, 0};
+          SPAN(0, 2.0 * T * Dv * R, gemm_bf16_tn(stream_, g));
+        }
+      } else {
         GemmRtArgs g{k.ctx, ldcx, (long)R, w.uv, (long)R, 1, (long)Dv * R, ov, ldov, (long)Dv, nullptr, T, Dv, R, H, f32};
         SPAN(5, 2.0 * T * H * Dv * R, gemm_rt(stream_, g));
       }

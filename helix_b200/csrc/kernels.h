@@ -334,6 +334,8 @@ cudaError_t latent_gather(cudaStream_t s, const bf16* cache, const int32_t* page
 // denominator; S and P have row stride ld, columns >= nk of P are written as zero
 cudaError_t latent_softmax(cudaStream_t s, const float* S, bf16* P, int ld, int rows, int H, int q0, int k0, int nk, int window,
                            float scale, const bf16* sink);
+// dst[h][r][d] = src[h][d][r] (bf16): the key up-projection per head, transposed once at load time
+cudaError_t transpose_heads_bf16(cudaStream_t s, const bf16* src, bf16* dst, int H, int Dk, int R);
 // out = o * sigmoid(g)
 cudaError_t sigmoid_gate(cudaStream_t s, const float* o, long ldo, const float* g, long ldg, float* out, bf16* out_b16, int T, int N);
 // f32 -> bf16 copy of a [T, N] block (row strides lds / ldd)

@@ -279,6 +279,8 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
       uint8_t* dkvn = own ? take(R) : nullptr;
       uint8_t* uk = take(H * Dk * R);
       uint8_t* uv = take(H * Dv * R);
+      uint8_t* ukT = d.compute_f32 ? nullptr : take(H * Dk * R);
+      w.ukT = ukT;
       uint8_t* sink = take(H);
       uint8_t* o = take(W * H * Dv);
       put(p + "mix.dq.norm", dqn, 0, Q, 1, true, 1.f);

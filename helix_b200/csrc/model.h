@@ -31,6 +31,7 @@ struct StackLayerW {
   int off_q = 0, off_k = 0, off_v = 0, off_g = 0, off_a1 = 0, off_dq = 0, off_dkv = -1;  // columns of the fused projection
   void *a2 = nullptr, *a2b = nullptr, *hnorm = nullptr;                                          // GLA
   void *dq_norm = nullptr, *uq = nullptr, *dkv_norm = nullptr, *uk = nullptr, *uv = nullptr, *sink = nullptr;  // LATENT
+  void* ukT = nullptr;  // LATENT, bf16 mode: [heads][kv_rank][dim] copy of uk (built after load; no checkpoint tensor)
   void* wo = nullptr;
   void *w_gu = nullptr, *b_gu = nullptr, *w_down = nullptr, *b_down = nullptr;  // feed-forward: rows [gate | up]
   size_t state_off = 0;  // GLA: float offset of this layer's [heads][dim][vdim] block inside a state slot

@@ -170,10 +170,22 @@ __global__ void sigmoid_gate_kernel(const float* __restrict__ o, long ldo, const
   if (outb) outb[(size_t)t * N + j] = __float2bfloat16(v);
 }
 
+// VEC = 4: N, both strides and both bases are multiples of four elements (16-byte loads, 8-byte stores)
+template <int VEC>
 __global__ void to_bf16_kernel(const float* __restrict__ src, long lds, bf16* __restrict__ dst, long ldd, int N) {
   const int t = blockIdx.y;
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j < N) dst[(size_t)t * ldd + j] = __float2bfloat16(src[(size_t)t * lds + j]);
+  const int j = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+  if (j >= N) return;
+  if (VEC == 4) {
+    const float4 v = *reinterpret_cast<const float4*>(src + (size_t)t * lds + j);
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<unsigned*>(&lo);
+    u.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(dst + (size_t)t * ldd + j) = u;
+  } else {
+    dst[(size_t)t * ldd + j] = __float2bfloat16(src[(size_t)t * lds + j]);
+  }
 }
 
 // ------------------------------------------------------------------ gated linear attention
@@ -249,16 +261,16 @@ __global__ void __launch_bounds__(128) gla_recurrence_kernel(GlaArgs a) {
       const float4* q4 = reinterpret_cast<const float4*>(tk);
       const float4* k4 = reinterpret_cast<const float4*>(tk + DKP);
       const float4* d4 = reinterpret_cast<const float4*>(tk + 2 * DKP);
-      float o = 0.f;
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;  // four chains: the dot product is not one 4*Dk-cycle dependency
 #pragma unroll
       for (int i = 0; i < DKP / 4; ++i) {
         const float4 q = q4[i], k = k4[i], d = d4[i];
-        S[4 * i + 0] = fmaf(d.x, S[4 * i + 0], k.x * vj); o = fmaf(S[4 * i + 0], q.x, o);
-        S[4 * i + 1] = fmaf(d.y, S[4 * i + 1], k.y * vj); o = fmaf(S[4 * i + 1], q.y, o);
-        S[4 * i + 2] = fmaf(d.z, S[4 * i + 2], k.z * vj); o = fmaf(S[4 * i + 2], q.z, o);
-        S[4 * i + 3] = fmaf(d.w, S[4 * i + 3], k.w * vj); o = fmaf(S[4 * i + 3], q.w, o);
+        S[4 * i + 0] = fmaf(d.x, S[4 * i + 0], k.x * vj); o0 = fmaf(S[4 * i + 0], q.x, o0);
+        S[4 * i + 1] = fmaf(d.y, S[4 * i + 1], k.y * vj); o1 = fmaf(S[4 * i + 1], q.y, o1);
+        S[4 * i + 2] = fmaf(d.z, S[4 * i + 2], k.z * vj); o2 = fmaf(S[4 * i + 2], q.z, o2);
+        S[4 * i + 3] = fmaf(d.w, S[4 * i + 3], k.w * vj); o3 = fmaf(S[4 * i + 3], q.w, o3);
       }
-      if (live) a.out[(size_t)(tc + tt) * a.ldo + (size_t)h * a.Dv + j] = o * a.q_scale;
+      if (live) a.out[(size_t)(tc + tt) * a.ldo + (size_t)h * a.Dv + j] = ((o0 + o1) + (o2 + o3)) * a.q_scale;
     }
     __syncthreads();  // the stage is rewritten by the copies issued in the next iteration
   }
@@ -455,6 +467,22 @@ __global__ void __launch_bounds__(kLatThreads) latent_attn_kernel(LatentAttnArgs
   }
 }
 
+// dst[h][r][d] = src[h][d][r]: per-head transposed copy of the key up-projection (bf16), so that carrying a query into the
+// latent space is a K-major product for the tensor-core GEMM
+__global__ void transpose_heads_kernel(const bf16* __restrict__ src, bf16* __restrict__ dst, int Dk, int R) {
+  const size_t h = blockIdx.z;
+  const int r = blockIdx.x * 32 + threadIdx.x, d0 = blockIdx.y * 32;
+  __shared__ bf16 tile[32][33];
+  for (int i = threadIdx.y; i < 32; i += blockDim.y)
+    if (d0 + i < Dk && r < R) tile[i][threadIdx.x] = src[(h * Dk + d0 + i) * R + r];
+  __syncthreads();
+  const int d = d0 + threadIdx.x;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int rr = blockIdx.x * 32 + i;
+    if (rr < R && d < Dk) dst[(h * R + rr) * Dk + d] = tile[threadIdx.x][i];
+  }
+}
+
 // block per key row jj
 __global__ void __launch_bounds__(128) latent_gather_kernel(const bf16* __restrict__ cache, const int32_t* __restrict__ pt, int page_size,
                                                             int k0, int nk, int R, int Dr, bf16* __restrict__ kbuf,
@@ -499,6 +527,10 @@ __global__ void __launch_bounds__(128) latent_softmax_kernel(const float* __rest
 
 #define KERR() cudaGetLastError()
 
+cudaError_t transpose_heads_bf16(cudaStream_t s, const bf16* src, bf16* dst, int H, int Dk, int R) {
+  transpose_heads_kernel<<<dim3((R + 31) / 32, (Dk + 31) / 32, H), dim3(32, 8), 0, s>>>(src, dst, Dk, R);
+  return KERR();
+}
 cudaError_t latent_gather(cudaStream_t s, const bf16* cache, const int32_t* pt, int page_size, int k0, int nk, int R, int Dr, bf16* kbuf,
                           bf16* ct, int ldk) {
   if (nk <= 0 || ldk < nk) return cudaErrorInvalidValue;
@@ -591,7 +623,10 @@ cudaError_t sigmoid_gate(cudaStream_t s, const float* o, long ldo, const float* 
 }
 cudaError_t to_bf16_rows(cudaStream_t s, const float* src, long lds, bf16* dst, long ldd, int T, int N) {
   if (T <= 0) return cudaSuccess;
-  to_bf16_kernel<<<dim3((N + 255) / 256, T), 256, 0, s>>>(src, lds, dst, ldd, N);
+  if (N % 4 == 0 && lds % 4 == 0 && ldd % 4 == 0 && ((uintptr_t)src & 15) == 0 && ((uintptr_t)dst & 7) == 0)
+    to_bf16_kernel<4><<<dim3((N / 4 + 255) / 256, T), 256, 0, s>>>(src, lds, dst, ldd, N);
+  else
+    to_bf16_kernel<1><<<dim3((N + 255) / 256, T), 256, 0, s>>>(src, lds, dst, ldd, N);
   return KERR();
 }
 
