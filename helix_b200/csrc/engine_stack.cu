@@ -136,13 +136,13 @@ static size_t stack_skinny_floats(const Model& m) {
 // latent layers.  Returns false when no layer qualifies (row sizes that are not 16-byte multiples).
 constexpr int kAttDenseMin = 64;
 static bool stack_att_caps(const Model& m, int* qb, size_t* rows, size_t* keys, size_t* rmax, size_t* dmax, size_t* qa16) {
-  *qb = 256; *rows = *keys = *rmax = *dmax = *qa16 = 0;
+  *qb = 512; *rows = *keys = *rmax = *dmax = *qa16 = 0;
   if (m.sd.compute_f32) return false;
   bool any = false;
   for (const hb_layer_desc& l : m.sl) {
     if (l.mixer != HB_MIXER_LATENT || (l.kv_rank + l.rot_dim) % 8 || l.kv_rank % 8) continue;
     any = true;
-    int q = 256;
+    int q = 512;
     while (q > 64 && (size_t)q * l.heads * (l.window + q) * 4 > (size_t(64) << 20)) q /= 2;  // scores of a block <= 64 MB
     *qb = std::min(*qb, q);
   }

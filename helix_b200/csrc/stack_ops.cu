@@ -145,19 +145,40 @@ __global__ void softcap_kernel(float* __restrict__ z, size_t n, float cap) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) z[i] = cap * tanhf(z[i] / cap);
 }
 
-template <typename WT>
+__device__ __forceinline__ float clamped_glu_one(float g, float u, float limit, float act_alpha) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g * sigmoidf_(act_alpha * g) * (u + 1.f);
+}
+// VEC = 4: F and ldg are multiples of four (16-byte loads and stores)
+template <typename WT, int VEC>
 __global__ void clamped_glu_kernel(const float* __restrict__ gu, long ldg, const WT* __restrict__ bg, const WT* __restrict__ bu,
                                    float limit, float act_alpha, float* __restrict__ out, bf16* __restrict__ outb, int F) {
   const int t = blockIdx.y;
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  const int j = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (j >= F) return;
-  float g = gu[(size_t)t * ldg + j] + (bg ? ldf<WT>(bg, j) : 0.f);
-  float u = gu[(size_t)t * ldg + F + j] + (bu ? ldf<WT>(bu, j) : 0.f);
-  g = fminf(g, limit);
-  u = fminf(fmaxf(u, -limit), limit);
-  const float v = g * sigmoidf_(act_alpha * g) * (u + 1.f);
-  out[(size_t)t * F + j] = v;
-  if (outb) outb[(size_t)t * F + j] = __float2bfloat16(v);
+  if (VEC == 4) {
+    const float4 g4 = *reinterpret_cast<const float4*>(gu + (size_t)t * ldg + j);
+    const float4 u4 = *reinterpret_cast<const float4*>(gu + (size_t)t * ldg + F + j);
+    const float g[4] = {g4.x, g4.y, g4.z, g4.w}, u[4] = {u4.x, u4.y, u4.z, u4.w};
+    float v[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      v[e] = clamped_glu_one(g[e] + (bg ? ldf<WT>(bg, j + e) : 0.f), u[e] + (bu ? ldf<WT>(bu, j + e) : 0.f), limit, act_alpha);
+    *reinterpret_cast<float4*>(out + (size_t)t * F + j) = make_float4(v[0], v[1], v[2], v[3]);
+    if (outb) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+      uint2 pk;
+      pk.x = *reinterpret_cast<unsigned*>(&lo);
+      pk.y = *reinterpret_cast<unsigned*>(&hi);
+      *reinterpret_cast<uint2*>(outb + (size_t)t * F + j) = pk;
+    }
+  } else {
+    const float v = clamped_glu_one(gu[(size_t)t * ldg + j] + (bg ? ldf<WT>(bg, j) : 0.f),
+                                    gu[(size_t)t * ldg + F + j] + (bu ? ldf<WT>(bu, j) : 0.f), limit, act_alpha);
+    out[(size_t)t * F + j] = v;
+    if (outb) outb[(size_t)t * F + j] = __float2bfloat16(v);
+  }
 }
 
 __global__ void sigmoid_gate_kernel(const float* __restrict__ o, long ldo, const float* __restrict__ g, long ldg,
@@ -610,9 +631,12 @@ cudaError_t softcap_rows(cudaStream_t s, float* logits, size_t n, float cap) {
 cudaError_t clamped_glu(cudaStream_t s, const float* gu, long ldg, const void* bg, const void* bu, bool f32, float limit,
                         float act_alpha, float* out, bf16* outb, int T, int F) {
   if (T <= 0) return cudaSuccess;
-  dim3 grid((F + 255) / 256, T);
-  if (f32) clamped_glu_kernel<float><<<grid, 256, 0, s>>>(gu, ldg, (const float*)bg, (const float*)bu, limit, act_alpha, out, outb, F);
-  else clamped_glu_kernel<bf16><<<grid, 256, 0, s>>>(gu, ldg, (const bf16*)bg, (const bf16*)bu, limit, act_alpha, out, outb, F);
+  const bool vec = F % 4 == 0 && ldg % 4 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)outb & 7) == 0;
+  dim3 grid(((vec ? F / 4 : F) + 255) / 256, T);
+  if (f32 && vec) clamped_glu_kernel<float, 4><<<grid, 256, 0, s>>>(gu, ldg, (const float*)bg, (const float*)bu, limit, act_alpha, out, outb, F);
+  else if (f32) clamped_glu_kernel<float, 1><<<grid, 256, 0, s>>>(gu, ldg, (const float*)bg, (const float*)bu, limit, act_alpha, out, outb, F);
+  else if (vec) clamped_glu_kernel<bf16, 4><<<grid, 256, 0, s>>>(gu, ldg, (const bf16*)bg, (const bf16*)bu, limit, act_alpha, out, outb, F);
+  else clamped_glu_kernel<bf16, 1><<<grid, 256, 0, s>>>(gu, ldg, (const bf16*)bg, (const bf16*)bu, limit, act_alpha, out, outb, F);
   return KERR();
 }
 
