@@ -221,9 +221,7 @@ __global__ void gla_decay_kernel(float* __restrict__ z, long ldz, const WT* __re
   z[(size_t)t * ldz + j] = expf(ls * inv_tau);
 }
 
-// One block per (entry, head, slice of value columns); thread j owns column j of the state (DKP >= Dk fp32 registers).
-// Tokens are staged through shared memory TCH at a time: q, k, decay of the head are the same for every thread.
-constexpr int kGlaTch = 16;
+constexpr int kGlaTch = 16;  // tokens per shared-memory stage of the recurrence
 __device__ __forceinline__ void cp_async4(float* smem_dst, const float* gsrc) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gsrc) : "memory");
@@ -231,22 +229,28 @@ __device__ __forceinline__ void cp_async4(float* smem_dst, const float* gsrc) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// Block = (entry, head, 32 value columns), DKP/16 warps: warp w owns key channels [16w, 16w+16) of the state (16 fp32
+// registers per thread), so a block of one slice still puts several warps on every scheduler.  Tokens are staged 16 at a
+// time through a cp.async double buffer; each warp leaves its partial dot products in shared memory and the block adds
+// them in warp order once per stage.
 template <int DKP>
-__global__ void __launch_bounds__(128) gla_recurrence_kernel(GlaArgs a) {
-  extern __shared__ float sm[];  // 2 stages x [kGlaTch][3 * DKP + blockDim.x]
+__global__ void __launch_bounds__(DKP * 2) gla_recurrence_kernel(GlaArgs a) {
+  constexpr int KS = DKP / 16;
+  constexpr int per_tok = 3 * DKP + 32, stage_floats = kGlaTch * per_tok;
+  extern __shared__ float sm[];  // 2 stages x [kGlaTch][3 * DKP + 32] + partial outputs [kGlaTch][KS][32]
+  float* obuf = sm + 2 * stage_floats;
   const int b = blockIdx.x, h = blockIdx.y;
-  const int c0 = blockIdx.z * blockDim.x;
-  const int j = c0 + threadIdx.x;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int j = blockIdx.z * 32 + lane;
   const bool live = j < a.Dv;
   const int t0 = a.cu[b], t1 = a.cu[b + 1];
-  const int Dk = a.Dk;
-  const int per_tok = 3 * DKP + blockDim.x, stage_floats = kGlaTch * per_tok;
+  const int Dk = a.Dk, i0 = w * 16;
   float* st = a.state + (size_t)a.slots[b] * a.slot_stride + (size_t)h * Dk * a.Dv;
-  float S[DKP];
+  float S[16];
   const bool fresh = a.first_pos[b] == 0;
 #pragma unroll
-  for (int i = 0; i < DKP; ++i) S[i] = (!fresh && live && i < Dk) ? st[(size_t)i * a.Dv + j] : 0.f;
-  // padded key channels read zeros: clear them once, the copies below only touch i < Dk
+  for (int i = 0; i < 16; ++i) S[i] = (!fresh && live && i0 + i < Dk) ? st[(size_t)(i0 + i) * a.Dv + j] : 0.f;
+  // padded key channels read zeros: clear the stages once, the copies below only touch i < Dk
   for (int e = threadIdx.x; e < 2 * stage_floats; e += blockDim.x) sm[e] = 0.f;
   __syncthreads();
   auto issue = [&](int tc, int stage) {
@@ -260,8 +264,10 @@ __global__ void __launch_bounds__(128) gla_recurrence_kernel(GlaArgs a) {
       cp_async4(dst + DKP + i, a.k + row * a.ld + h * Dk + i);
       cp_async4(dst + 2 * DKP + i, a.decay + row * a.ldd + h * Dk + i);
     }
-    if (live)
-      for (int tt = 0; tt < nt; ++tt) cp_async4(base + tt * per_tok + 3 * DKP + threadIdx.x, a.v + (size_t)(tc + tt) * a.ld + (size_t)h * a.Dv + j);
+    for (int e = threadIdx.x; e < nt * 32; e += blockDim.x) {
+      const int tt = e >> 5, c = e & 31;
+      if (blockIdx.z * 32 + c < a.Dv) cp_async4(base + tt * per_tok + 3 * DKP + c, a.v + (size_t)(tc + tt) * a.ld + (size_t)h * a.Dv + blockIdx.z * 32 + c);
+    }
     cp_async_commit();
   };
   if (t0 < t1) issue(t0, 0);
@@ -278,27 +284,35 @@ __global__ void __launch_bounds__(128) gla_recurrence_kernel(GlaArgs a) {
     const float* base = sm + stage * stage_floats;
     for (int tt = 0; tt < nt; ++tt) {
       const float* tk = base + tt * per_tok;
-      const float vj = tk[3 * DKP + threadIdx.x];
-      const float4* q4 = reinterpret_cast<const float4*>(tk);
-      const float4* k4 = reinterpret_cast<const float4*>(tk + DKP);
-      const float4* d4 = reinterpret_cast<const float4*>(tk + 2 * DKP);
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;  // four chains: the dot product is not one 4*Dk-cycle dependency
+      const float vj = tk[3 * DKP + lane];
+      const float4* q4 = reinterpret_cast<const float4*>(tk + i0);
+      const float4* k4 = reinterpret_cast<const float4*>(tk + DKP + i0);
+      const float4* d4 = reinterpret_cast<const float4*>(tk + 2 * DKP + i0);
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-      for (int i = 0; i < DKP / 4; ++i) {
+      for (int i = 0; i < 4; ++i) {
         const float4 q = q4[i], k = k4[i], d = d4[i];
         S[4 * i + 0] = fmaf(d.x, S[4 * i + 0], k.x * vj); o0 = fmaf(S[4 * i + 0], q.x, o0);
         S[4 * i + 1] = fmaf(d.y, S[4 * i + 1], k.y * vj); o1 = fmaf(S[4 * i + 1], q.y, o1);
         S[4 * i + 2] = fmaf(d.z, S[4 * i + 2], k.z * vj); o2 = fmaf(S[4 * i + 2], q.z, o2);
         S[4 * i + 3] = fmaf(d.w, S[4 * i + 3], k.w * vj); o3 = fmaf(S[4 * i + 3], q.w, o3);
       }
-      if (live) a.out[(size_t)(tc + tt) * a.ldo + (size_t)h * a.Dv + j] = ((o0 + o1) + (o2 + o3)) * a.q_scale;
+      obuf[(tt * KS + w) * 32 + lane] = (o0 + o1) + (o2 + o3);
     }
-    __syncthreads();  // the stage is rewritten by the copies issued in the next iteration
+    __syncthreads();
+    for (int e = threadIdx.x; e < nt * 32; e += blockDim.x) {
+      const int tt = e >> 5, c = e & 31;
+      float o = 0.f;
+#pragma unroll
+      for (int ww = 0; ww < KS; ++ww) o += obuf[(tt * KS + ww) * 32 + c];
+      if (blockIdx.z * 32 + c < a.Dv) a.out[(size_t)(tc + tt) * a.ldo + (size_t)h * a.Dv + blockIdx.z * 32 + c] = o * a.q_scale;
+    }
+    __syncthreads();  // the stage and the partial outputs are rewritten in the next iteration
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < DKP; ++i)
-      if (i < Dk) st[(size_t)i * a.Dv + j] = S[i];
+    for (int i = 0; i < 16; ++i)
+      if (i0 + i < Dk) st[(size_t)(i0 + i) * a.Dv + j] = S[i];
   }
 }
 
@@ -574,10 +588,10 @@ cudaError_t stack_ops_init() {
   HB_SMEM(postnorm_kernel<bf16>, big);
   HB_SMEM((latent_attn_kernel<float, float>), big);
   HB_SMEM((latent_attn_kernel<bf16, bf16>), big);
-  HB_SMEM(gla_recurrence_kernel<16>, 64 * 1024);
-  HB_SMEM(gla_recurrence_kernel<32>, 64 * 1024);
-  HB_SMEM(gla_recurrence_kernel<64>, 64 * 1024);
-  HB_SMEM(gla_recurrence_kernel<128>, 64 * 1024);
+  HB_SMEM(gla_recurrence_kernel<16>, 80 * 1024);
+  HB_SMEM(gla_recurrence_kernel<32>, 80 * 1024);
+  HB_SMEM(gla_recurrence_kernel<64>, 80 * 1024);
+  HB_SMEM(gla_recurrence_kernel<128>, 80 * 1024);
 #undef HB_SMEM
   return cudaSuccess;
 }
@@ -664,13 +678,10 @@ cudaError_t gla_decay(cudaStream_t s, float* z, long ldz, const void* bias, bool
 
 template <int DKP>
 static cudaError_t gla_launch(cudaStream_t s, const GlaArgs& a) {
-  // value columns per block: as wide as possible while the grid still covers the machine twice (the recurrence is serial
-  // in the tokens of an entry, so parallelism comes from entries x heads x column slices only)
-  int cols = std::min(128, (a.Dv + 31) / 32 * 32);
-  while (cols > 32 && (long)a.B * a.H * ((a.Dv + cols - 1) / cols) < 2 * 148) cols /= 2;
-  dim3 grid(a.B, a.H, (a.Dv + cols - 1) / cols);
-  const size_t smem = (size_t)2 * kGlaTch * (3 * DKP + cols) * 4;  // <= 2 * 16 * 512 * 4 = 64 KB
-  gla_recurrence_kernel<DKP><<<grid, cols, smem, s>>>(a);
+  constexpr int KS = DKP / 16;
+  dim3 grid(a.B, a.H, (a.Dv + 31) / 32);
+  const size_t smem = (size_t)(2 * kGlaTch * (3 * DKP + 32) + kGlaTch * KS * 32) * 4;  // <= 69 KB at DKP = 128
+  gla_recurrence_kernel<DKP><<<grid, 32 * KS, smem, s>>>(a);
   return KERR();
 }
 cudaError_t gla_recurrence(cudaStream_t s, const GlaArgs& a) {
