@@ -140,6 +140,58 @@ __global__ void __launch_bounds__(256) postnorm_kernel(const float* __restrict__
   }
 }
 
+// The same step with the row held in registers as float4 (W a multiple of 4, W <= 4 * 256 * kPnChunks)
+constexpr int kPnChunks = 8;
+template <typename WT>
+__global__ void __launch_bounds__(256) postnorm_vec_kernel(const float* __restrict__ x, const int32_t* __restrict__ row_index,
+                                                           const float* __restrict__ y, long ldy, const WT* __restrict__ bias,
+                                                           const WT* __restrict__ w, float alpha, float off, float eps,
+                                                           float* __restrict__ out, bf16* __restrict__ outb, int W) {
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const size_t src = row_index ? (size_t)row_index[r] : (size_t)r;
+  const int nv = W / 4;
+  float4 v[kPnChunks];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < kPnChunks; ++c) {
+    const int i = threadIdx.x + c * 256;
+    if (i < nv) {
+      float4 a = *reinterpret_cast<const float4*>(x + src * W + 4 * i);
+      if (y) {
+        const float4 b = *reinterpret_cast<const float4*>(y + (size_t)r * ldy + 4 * i);
+        a.x = alpha * a.x + b.x + (bias ? ldf<WT>(bias, 4 * i) : 0.f);
+        a.y = alpha * a.y + b.y + (bias ? ldf<WT>(bias, 4 * i + 1) : 0.f);
+        a.z = alpha * a.z + b.z + (bias ? ldf<WT>(bias, 4 * i + 2) : 0.f);
+        a.w = alpha * a.w + b.w + (bias ? ldf<WT>(bias, 4 * i + 3) : 0.f);
+      }
+      v[c] = a;
+      ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+    }
+  }
+  ss = block_sum(ss, red);
+  const float rs = 1.f / sqrtf(ss / (float)W + eps);
+#pragma unroll
+  for (int c = 0; c < kPnChunks; ++c) {
+    const int i = threadIdx.x + c * 256;
+    if (i < nv) {
+      float4 a = v[c];
+      a.x *= rs * (off + ldf<WT>(w, 4 * i));
+      a.y *= rs * (off + ldf<WT>(w, 4 * i + 1));
+      a.z *= rs * (off + ldf<WT>(w, 4 * i + 2));
+      a.w *= rs * (off + ldf<WT>(w, 4 * i + 3));
+      *reinterpret_cast<float4*>(out + (size_t)r * W + 4 * i) = a;
+      if (outb) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
+        uint2 pk;
+        pk.x = *reinterpret_cast<unsigned*>(&lo);
+        pk.y = *reinterpret_cast<unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(outb + (size_t)r * W + 4 * i) = pk;
+      }
+    }
+  }
+}
+
 __global__ void softcap_kernel(float* __restrict__ z, size_t n, float cap) {
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) z[i] = cap * tanhf(z[i] / cap);
@@ -618,6 +670,14 @@ cudaError_t embed_rows_f32(cudaStream_t s, const int32_t* tokens, const void* ta
 static cudaError_t postnorm_launch(cudaStream_t s, const float* x, const int32_t* idx, const float* y, long ldy, const void* bias,
                                    const void* w, bool f32, float alpha, float off, float eps, float* out, bf16* outb, int rows, int W) {
   if (rows <= 0) return cudaSuccess;
+  if (W % 4 == 0 && W <= 4 * 256 * kPnChunks && (!y || ldy % 4 == 0) && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0 &&
+      ((uintptr_t)out & 15) == 0 && ((uintptr_t)outb & 7) == 0) {
+    if (f32)
+      postnorm_vec_kernel<float><<<rows, 256, 0, s>>>(x, idx, y, ldy, (const float*)bias, (const float*)w, alpha, off, eps, out, outb, W);
+    else
+      postnorm_vec_kernel<bf16><<<rows, 256, 0, s>>>(x, idx, y, ldy, (const bf16*)bias, (const bf16*)w, alpha, off, eps, out, outb, W);
+    return KERR();
+  }
   const size_t smem = (size_t)(W + 32) * 4;
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
   if (f32)

@@ -55,6 +55,8 @@ CONFIGS = {
     "mixed_shared": dict(),
     "one_head_alpha1": dict(alpha=1.0, gla=dict(heads=1, dim=32, vdim=8), lat=dict(heads=1, dim=8, vdim=16, window=7), cap=0.0),
     "ff_everywhere": dict(order=("gla", "latent_attention", "gla"), mlp_on=("gla", "latent_attention"), gla=dict(heads=2, dim=40, vdim=72)),
+    # nothing a multiple of 8 or 4: every product takes the CUDA-core GEMM, rows are loaded element by element
+    "odd_sizes": dict(width=90, gla=dict(heads=2, dim=12, vdim=20), lat=dict(heads=2, dim=12, vdim=20, kv_rank=28, q_rank=20, rot_dim=6, window=9), ff=50),
     "wide_rows": dict(width=128, vocab=256, lat=dict(heads=5, dim=16, vdim=8, kv_rank=72, q_rank=24, rot_dim=8, window=65), ff=64),
 }
 
