@@ -165,14 +165,13 @@ static size_t carve(Model* m, const hb_model_desc& d, uint8_t* base) {
 std::string validate_stack(const hb_stack_desc& d, const hb_layer_desc* L) {
   if (!L) return "no layer list";
   if (d.width <= 0 || d.vocab <= 0 || d.n_layers <= 0) return "non-positive dimension";
-  if (d.vocab % 4) return "vocab must be a multiple of 4 (16-byte rows of the fp32 logits)";
   if (!(d.norm_eps > 0.f)) return "norm_eps must be positive";
   for (int i = 0; i < d.n_layers; ++i) {
     const hb_layer_desc& l = L[i];
     const std::string at = " (layer " + std::to_string(i) + ")";
     if (l.heads <= 0 || l.dim <= 0 || l.vdim <= 0) return "non-positive head size" + at;
     if (l.mixer == HB_MIXER_GLA) {
-      if (l.dim > 128) return "GLA key channels per head > 128 unsupported (register-resident state column)" + at;
+      if (l.dim > 256) return "GLA key channels per head > 256 unsupported (one warp per 16 channels, 512 threads per block)" + at;
       if (!(l.tau > 0.f) || l.decay_rank <= 0) return "GLA needs tau > 0 and a decay rank" + at;
     } else if (l.mixer == HB_MIXER_LATENT) {
       if (l.q_rank <= 0 || l.kv_rank <= 0 || l.rot_dim < 0 || l.window <= 0) return "latent attention sizes" + at;

@@ -644,6 +644,7 @@ cudaError_t stack_ops_init() {
   HB_SMEM(gla_recurrence_kernel<32>, 80 * 1024);
   HB_SMEM(gla_recurrence_kernel<64>, 80 * 1024);
   HB_SMEM(gla_recurrence_kernel<128>, 80 * 1024);
+  HB_SMEM(gla_recurrence_kernel<256>, 160 * 1024);
 #undef HB_SMEM
   return cudaSuccess;
 }
@@ -740,7 +741,7 @@ template <int DKP>
 static cudaError_t gla_launch(cudaStream_t s, const GlaArgs& a) {
   constexpr int KS = DKP / 16;
   dim3 grid(a.B, a.H, (a.Dv + 31) / 32);
-  const size_t smem = (size_t)(2 * kGlaTch * (3 * DKP + 32) + kGlaTch * KS * 32) * 4;  // <= 69 KB at DKP = 128
+  const size_t smem = (size_t)(2 * kGlaTch * (3 * DKP + 32) + kGlaTch * KS * 32) * 4;  // 65 KB at DKP = 128, 131 KB at 256
   gla_recurrence_kernel<DKP><<<grid, 32 * KS, smem, s>>>(a);
   return KERR();
 }
@@ -750,7 +751,8 @@ cudaError_t gla_recurrence(cudaStream_t s, const GlaArgs& a) {
   if (a.Dk <= 32) return gla_launch<32>(s, a);
   if (a.Dk <= 64) return gla_launch<64>(s, a);
   if (a.Dk <= 128) return gla_launch<128>(s, a);
-  return cudaErrorInvalidValue;  // key channels per head beyond the register-resident state column
+  if (a.Dk <= 256) return gla_launch<256>(s, a);
+  return cudaErrorInvalidValue;  // more key channels per head than one block's warps cover
 }
 
 cudaError_t headnorm_silu_gate(cudaStream_t s, const float* o, long ldo, const float* g, long ldg, const void* w, bool f32, float eps,

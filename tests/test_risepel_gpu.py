@@ -57,6 +57,8 @@ CONFIGS = {
     "ff_everywhere": dict(order=("gla", "latent_attention", "gla"), mlp_on=("gla", "latent_attention"), gla=dict(heads=2, dim=40, vdim=72)),
     # nothing a multiple of 8 or 4: every product takes the CUDA-core GEMM, rows are loaded element by element
     "odd_sizes": dict(width=90, gla=dict(heads=2, dim=12, vdim=20), lat=dict(heads=2, dim=12, vdim=20, kv_rank=28, q_rank=20, rot_dim=6, window=9), ff=50),
+    # a vocabulary that is no multiple of 4, 200 key channels per GLA head (the widest state block), one value column
+    "wide_state": dict(vocab=131, gla=dict(heads=1, dim=200, vdim=33), order=("gla", "latent_attention"), lat=dict(window=3)),
     "wide_rows": dict(width=128, vocab=256, lat=dict(heads=5, dim=16, vdim=8, kv_rank=72, q_rank=24, rot_dim=8, window=65), ff=64),
 }
 
