@@ -47,12 +47,12 @@ def tiny_bert(layers=2, vocab=1000):
                      max_pos=512, type_vocab=2, norm_eps=1e-12)
 
 
-def risepel_stack(width, layers, ff=None, window=512, pattern=("gla", "gla", "latent"), vocab=32768, compute_f32=False):
+def risepel_stack(width, layers, ff=None, window=512, pattern=("gla", "latent", "gla", "gla"), vocab=32768, compute_f32=False):
     """A Risepel-design stack at sizes that resemble a served model's layers (random-init benchmarks): per width, heads of
     128 value channels; GLA layers with 64 key channels per head and a rank-64 decay projection; latent-attention layers with
-    a 512-wide cache latent, 64 rotary dims, queries through a width/4 latent, a sliding window, a feed-forward after every
-    attention layer (the pattern of the design's checkpoints: two recurrent layers, then attention + feed-forward, with
-    every second attention layer reading the cache rows of the one before)."""
+    a 512-wide cache latent, 64 rotary dims, queries through a width/4 latent, a sliding window and a feed-forward after
+    every attention layer; one layer in four is attention, every second attention layer reads the cache rows of the one
+    before it."""
     from .engine import LayerDesc, StackDesc, MIXER_GLA, MIXER_LATENT
     heads = max(1, width // 128)
     ff = ff or (width * 4)

@@ -46,7 +46,7 @@
 extern "C" {
 #endif
 
-#define HB_ABI_VERSION 2
+#define HB_ABI_VERSION 3
 
 typedef enum hb_status {
   HB_OK = 0,

@@ -244,7 +244,7 @@ func (r *B200Runtime) Warm(ctx context.Context, _ string) error {
 
 func (r *B200Runtime) ListModels(context.Context) ([]string, error) { return []string{r.p.Model}, nil }
 func (r *B200Runtime) Version() string {
-	return "helix-b200/0.2 (abi " + strconv.Itoa(int(C.hb_abi_version())) + ")"
+	return "helix-b200/0.3 (abi " + strconv.Itoa(int(C.hb_abi_version())) + ")"
 }
 func (r *B200Runtime) Runtime() types.Runtime { return types.RuntimeVLLM } // Option A, SURVEY.md §8b
 func (r *B200Runtime) URL() string            { return r.front.URL() }

@@ -26,12 +26,12 @@ def test_library_exports_every_declared_symbol():
     missing = [n for n in sorted(decl) if not hasattr(l, n)]
     assert not missing, missing
     assert decl == set(_lib.SIGNATURES), (decl ^ set(_lib.SIGNATURES))
-    assert l.hb_abi_version() == 2
+    assert l.hb_abi_version() == 3
 
 
 def test_struct_sizes_match_header_layout():
     import ctypes as C
-    assert C.sizeof(_lib.EngineCfg) == 64 and C.sizeof(_lib.ModelDescC) == 100
+    assert C.sizeof(_lib.EngineCfg) == 72 and C.sizeof(_lib.ModelDescC) == 100
     assert C.sizeof(_lib.SamplingC) == 64
 
 
@@ -41,7 +41,8 @@ def test_ctypes_layouts_match_the_c_header_field_by_field(tmp_path):
     import ctypes as C
     import subprocess
     structs = {"hb_engine_cfg": _lib.EngineCfg, "hb_model_desc": _lib.ModelDescC, "hb_sampling": _lib.SamplingC,
-               "hb_stats": _lib.StatsC}
+               "hb_stats": _lib.StatsC, "hb_layer_desc": _lib.LayerDescC, "hb_stack_desc": _lib.StackDescC,
+               "hb_seq_feed": _lib.SeqFeedC}
     lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "helix_b200.h"', 'int main(void) {']
     for cname, ct in structs.items():
         lines.append(f'  printf("{cname} %zu\\n", sizeof({cname}));')
