@@ -3,6 +3,7 @@ from .engine import ModelDesc
 
 LLAMA = 0
 BERT = 1
+RISEPEL = 2  # layer-list decoders (engine.StackDesc)
 
 
 def llama3_8b():

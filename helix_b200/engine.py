@@ -120,6 +120,10 @@ class StackDesc:
     def hidden(self):
         return self.width
 
+    @property
+    def max_pos(self):
+        return 1 << 20  # rotary angles and the recurrence are computed per position: no trained position limit
+
     def to_c(self):
         arr = (LayerDescC * len(self.layers))(*[l.to_c() for l in self.layers])
         return StackDescC(self.width, self.vocab, len(self.layers), self.compute_f32, self.norm_eps, self.resid_alpha,

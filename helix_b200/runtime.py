@@ -5,6 +5,8 @@ rendering of this file.  Plug-in "Option A" of SURVEY.md §8b: the slot keeps `r
 and the scheduler's vLLM-style args arrive unchanged (`--gpu-memory-utilization`, `--max-num-seqs`,
 `--max-model-len`, `--task embed`; api/pkg/scheduler/runner.go:1187-1259,1344-1397).
 """
+import glob
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Callable, List, Optional
@@ -144,6 +146,14 @@ class B200Runtime:
         Stop, slot.go:113-140)."""
         desc = self.p.desc
         embed = self.parsed.task_embed
+        ckpt = None
+        if desc is None and os.path.isfile(os.path.join(self.p.model, "config.json")):
+            # a checkpoint folder (config.json + *.safetensors): the model class comes from its configuration
+            from . import weights_io
+            ckpt = sorted(glob.glob(os.path.join(self.p.model, "*.safetensors")))
+            if not ckpt:
+                raise HBError(-5, f"no .safetensors file in {self.p.model!r}")
+            desc = weights_io.desc_from_hf_config(os.path.join(self.p.model, "config.json"), weights_io.safetensors_shapes(ckpt))
         if desc is None:
             if self.p.model not in MODEL_CATALOGUE:
                 raise HBError(-5, f"model {self.p.model!r} is not in the B200 runtime catalogue")
@@ -159,11 +169,14 @@ class B200Runtime:
                            decode_with_prefill=1)  # running streams keep decoding while long prompts are prefilled
         eng = (self.p.engine_factory or Engine)(cfg)
         try:
-            if self.p.state_dict is not None:
+            if ckpt is not None:
+                from . import weights_io
+                weights_io.load_safetensors(eng, desc, ckpt)
+            elif self.p.state_dict is not None:
                 eng.load_state_dict(desc, self.p.state_dict)
             else:
                 eng.load_random(desc, self.p.seed)
-            if desc.arch == configs.LLAMA:
+            if desc.arch in (configs.LLAMA, configs.RISEPEL):
                 eng.start()
             self.engine = eng
             self.is_embed = embed or desc.arch == configs.BERT

@@ -288,3 +288,48 @@ def test_random_weights_and_bad_descriptions():
     with hb.Engine(hb.EngineConfig(device=0, max_seqs=2, max_ctx=128, max_batched_tokens=128)) as e:
         with pytest.raises(hb.HBError):
             e.load_random(bad, seed=5)
+
+
+def test_tensor_core_head_products_and_long_windows():
+    # steps of > 256 tokens with head sizes the tcgen05 GEMM takes: absorption / value expansion per head on the tensor
+    # cores, attention of the portion as dense products over a window longer than a query block's own tokens
+    cfg = ref.random_config(width=128, order=("latent_attention", "gla", "latent_attention"),
+                            lat=dict(heads=2, dim=64, vdim=64, kv_rank=64, q_rank=64, rot_dim=16, window=300), ff=128)
+    sd = ref.random_state_dict(cfg, seed=41)
+    toks = tokens(8, 700, cfg["vocab"])
+    want = ref.RisepelOracle(cfg, sd).forward(toks)
+    for f32 in (1, 0):
+        with make_engine(cfg, sd, f32, ctx=768) as e:
+            assert row_err(replay(e, toks, [len(toks)]), want).max() < TOL[f32]
+            assert row_err(replay(e, toks, [290, 300, 70, 38]), want).max() < TOL[f32]
+
+
+def test_runtime_serves_a_checkpoint_folder(tmp_path):
+    import json
+    from helix_b200.runtime import B200Runtime, B200RuntimeParams
+    cfg = ref.random_config(vocab=200)
+    sd = ref.random_state_dict(cfg, seed=43)
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    weights_io.write_safetensors(tmp_path / "model.safetensors", sd)
+    rt = B200Runtime(B200RuntimeParams(model=str(tmp_path), context_length=256, serve_http=False,
+                                       args=["--max-num-seqs", "4", "--max-num-batched-tokens", "256"]))
+    rt.start()
+    try:
+        e = rt.engine
+        prompt = tokens(9, 50, cfg["vocab"])
+        rid = e.submit(prompt, hb.Sampling(max_tokens=8, capture=CAPTURE_STEP_LOGITS))
+        out, fin = [], 0
+        while not fin:
+            assert e.wait(rid, 20000)
+            t, fin = e.poll(rid)
+            out += t
+        rows = e.captured_logits(rid, CAPTURE_STEP_LOGITS)
+        o = ref.RisepelOracle(cfg, sd)
+        st = o.new_state()
+        z = o.forward(prompt, st)[-1]
+        for k, t in enumerate(out):  # teacher-forced on the engine's own ids (serving mode)
+            assert row_err(rows[k][None], z[None]).max() < TOL[0]
+            z = o.forward([t], st)[-1]
+        assert len(out) == 8
+    finally:
+        rt.stop()
