@@ -177,7 +177,7 @@ std::string validate_stack(const hb_stack_desc& d, const hb_layer_desc* L) {
       if (l.q_rank <= 0 || l.kv_rank <= 0 || l.rot_dim < 0 || l.window <= 0) return "latent attention sizes" + at;
       if (l.rope_dims < 0 || l.rope_dims % 2 || l.rope_dims > l.rot_dim) return "rope_dims must be even and <= rot_dim" + at;
       if (l.rope_dims > 0 && !(l.rope_base > 0.f)) return "rope_base must be positive" + at;
-      if ((size_t)(l.kv_rank + l.rot_dim + 2 * l.window + 1024 + 40) * 4 > 200 * 1024) return "window + latent row exceed the attention kernel's shared memory" + at;
+      if ((size_t)(4 * (l.kv_rank + l.rot_dim + 4) + 5 * l.window + 8 * 1024 + 136) * 4 > 200 * 1024) return "window + latent row exceed the attention kernel's shared memory" + at;
       if (l.kv_from >= 0) {
         if (l.kv_from >= i) return "kv_from must name an earlier layer" + at;
         const hb_layer_desc& s = L[l.kv_from];

@@ -38,15 +38,6 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   float t = (l < nw) ? red[l] : 0.f;
   return warp_sum(t);
 }
-__device__ __forceinline__ float block_max(float v, float* red) {
-  v = warp_max(v);
-  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
-  __syncthreads();
-  if (l == 0) red[w] = v;
-  __syncthreads();
-  float t = (l < nw) ? red[l] : -INFINITY;
-  return warp_max(t);
-}
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-z)); }
 
 // ------------------------------------------------------------------ CUDA-core GEMM
@@ -455,101 +446,211 @@ __global__ void latent_q_rope_kernel(const float* __restrict__ q, long ldq, floa
   }
 }
 
-// One block per (token, head), kLatThreads threads.  dynamic smem: q [R+Dr] + scores [window] + partial sums [threads] + 32.
-// Scores: one warp per key (16-byte loads of bf16 rows when the row length allows).  Weighted sum: thread (g, r) adds the
-// keys jj = g mod G of latent entry r, groups are then summed in group order — fixed per (R, threads), independent of the batch.
+// One block per (token, group of kLatHG heads), kLatThreads threads.  Every head of a token reads the same cache rows, so a
+// block serves several heads from one pass over them.  dynamic smem: q [HG][D] + scores [window][HG] + page-resolved row
+// index [window] + group partials [threads][HG] + 32.
+// Scores: one warp per key (16-byte loads of bf16 rows when the row length allows), HG dot products per loaded row.
+// Weighted sum: thread (g, r) adds the keys jj = g mod G of latent entry r for all HG heads; groups are then summed in group
+// order — fixed per (R, threads), independent of the batch.
 constexpr int kLatThreads = 1024;
-__device__ __forceinline__ float dot_row(const float* __restrict__ qs, const float* __restrict__ row, int D, int l) {
-  float s = 0.f;
-  for (int i = l; i < D; i += 32) s = fmaf(qs[i], row[i], s);
-  return s;
-}
-__device__ __forceinline__ float dot_row(const float* __restrict__ qs, const bf16* __restrict__ row, int D, int l) {
-  float s = 0.f;
-  if ((D & 7) == 0) {  // rows start on 16-byte boundaries
-    for (int i = l * 8; i < D; i += 256) {
-      const uint4 u = *reinterpret_cast<const uint4*>(row + i);
-      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f = __bfloat1622float2(p2[e]);
-        s = fmaf(qs[i + 2 * e], f.x, s);
-        s = fmaf(qs[i + 2 * e + 1], f.y, s);
-      }
-    }
-  } else {
-    for (int i = l; i < D; i += 32) s = fmaf(qs[i], __bfloat162float(row[i]), s);
-  }
-  return s;
-}
+constexpr int kLatHG = 4;
 template <typename WT, typename CT>
 __global__ void __launch_bounds__(kLatThreads) latent_attn_kernel(LatentAttnArgs a) {
+  constexpr int HG = kLatHG;
   extern __shared__ float sm[];
-  const int D = a.R + a.Dr;
-  float* qs = sm;
-  float* sc = sm + (D + 3) / 4 * 4;
-  float* part = sc + a.window;
-  float* red = part + blockDim.x;
-  int* rowoff = reinterpret_cast<int*>(red + 32);  // cache row of every visible key (page lookup done once)
-  const int t = blockIdx.x, h = blockIdx.y;
+  const int D = a.R + a.Dr, Dp = (D + 3) / 4 * 4;
+  float* qs = sm;                       // [HG][Dp]
+  float* sc = qs + HG * Dp;             // [window][HG]
+  float* part = sc + HG * a.window;     // [8 * threads]: group partials of the weighted sum
+  float* red = part + 8 * blockDim.x;   // [32 * HG]
+  int* rowoff = reinterpret_cast<int*>(red + 32 * HG);  // [window] cache row of every visible key (page lookup done once)
+  const int t = blockIdx.x, h0 = blockIdx.y * HG;
+  const int nh = min(HG, a.H - h0);
   const int pos = a.positions[t];
   const int n = min(pos + 1, a.window), j0 = pos - n + 1;  // keys j0 .. pos
   const int32_t* pt = a.page_table + (size_t)a.seq_of[t] * a.max_pages;
   const CT* cache = (const CT*)a.cache;
-  for (int i = threadIdx.x; i < D; i += blockDim.x) qs[i] = a.qabs[(size_t)t * a.ldqa + (size_t)h * D + i];
+  for (int e = threadIdx.x; e < HG * Dp; e += blockDim.x) {
+    const int hh = e / Dp, i = e % Dp;
+    qs[e] = (hh < nh && i < D) ? a.qabs[(size_t)t * a.ldqa + (size_t)(h0 + hh) * D + i] : 0.f;
+  }
   for (int jj = threadIdx.x; jj < n; jj += blockDim.x) {
     const int j = j0 + jj;
     rowoff[jj] = pt[j / a.page_size] * a.page_size + j % a.page_size;
   }
   __syncthreads();
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
-  for (int jj = w; jj < n; jj += nw) {
+  if (sizeof(CT) == 2 && (D & 7) == 0) {
+    // bf16 rows that start on 16-byte boundaries: two keys per iteration, their loads issued together
+    for (int jj = w; jj < n; jj += 2 * nw) {
+      const int jb = jj + nw;
+      const bool two = jb < n;
+      const bf16* ra = reinterpret_cast<const bf16*>(cache) + (size_t)rowoff[jj] * D;
+      const bf16* rb = reinterpret_cast<const bf16*>(cache) + (size_t)rowoff[two ? jb : jj] * D;
+      float sa[HG] = {}, sb[HG] = {};
+      for (int i = l * 8; i < D; i += 256) {
+        const uint4 ua = *reinterpret_cast<const uint4*>(ra + i), ub = *reinterpret_cast<const uint4*>(rb + i);
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&ua);
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&ub);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 fa = __bfloat1622float2(pa[e]), fb = __bfloat1622float2(pb[e]);
+#pragma unroll
+          for (int hh = 0; hh < HG; ++hh) {
+            const float2 q = *reinterpret_cast<const float2*>(qs + hh * Dp + i + 2 * e);
+            sa[hh] = fmaf(q.x, fa.x, sa[hh]); sa[hh] = fmaf(q.y, fa.y, sa[hh]);
+            sb[hh] = fmaf(q.x, fb.x, sb[hh]); sb[hh] = fmaf(q.y, fb.y, sb[hh]);
+          }
+        }
+      }
+#pragma unroll
+      for (int hh = 0; hh < HG; ++hh) {
+        sa[hh] = warp_sum(sa[hh]);
+        sb[hh] = warp_sum(sb[hh]);
+      }
+      if (l == 0) {
+#pragma unroll
+        for (int hh = 0; hh < HG; ++hh) {
+          sc[jj * HG + hh] = sa[hh] * a.scale;
+          if (two) sc[jb * HG + hh] = sb[hh] * a.scale;
+        }
+      }
+    }
+  }
+  for (int jj = (sizeof(CT) == 2 && (D & 7) == 0) ? n : w; jj < n; jj += nw) {  // rows read element by element
     const CT* row = cache + (size_t)rowoff[jj] * D;
-    const float s = warp_sum(dot_row(qs, row, D, l));
-    if (l == 0) sc[jj] = s * a.scale;
+    float s[HG] = {};
+    for (int i = l; i < D; i += 32) {
+      const float kv = ldf<CT>(row, i);
+#pragma unroll
+      for (int hh = 0; hh < HG; ++hh) s[hh] = fmaf(qs[hh * Dp + i], kv, s[hh]);
+    }
+#pragma unroll
+    for (int hh = 0; hh < HG; ++hh) s[hh] = warp_sum(s[hh]);
+    if (l == 0) {
+#pragma unroll
+      for (int hh = 0; hh < HG; ++hh) sc[jj * HG + hh] = s[hh] * a.scale;
+    }
   }
   __syncthreads();
-  const float sink = ldf<WT>((const WT*)a.sink, h);
-  float m = sink;
-  for (int jj = threadIdx.x; jj < n; jj += blockDim.x) m = fmaxf(m, sc[jj]);
-  m = block_max(m, red);
-  float sum = 0.f;
+  // fp32 softmax with the sink in the denominator; the HG heads share each block reduction
+  float inv[HG], mx[HG], sink[HG];
+#pragma unroll
+  for (int hh = 0; hh < HG; ++hh) mx[hh] = sink[hh] = hh < nh ? ldf<WT>((const WT*)a.sink, h0 + hh) : 0.f;
   for (int jj = threadIdx.x; jj < n; jj += blockDim.x) {
-    const float e = expf(sc[jj] - m);
-    sc[jj] = e;
-    sum += e;
+    const float4 v = *reinterpret_cast<const float4*>(sc + jj * HG);
+    mx[0] = fmaxf(mx[0], v.x); mx[1] = fmaxf(mx[1], v.y); mx[2] = fmaxf(mx[2], v.z); mx[3] = fmaxf(mx[3], v.w);
   }
-  sum = block_sum(sum, red) + expf(sink - m);  // block_sum's barriers also publish sc[]
-  const float inv = 1.f / sum;
+#pragma unroll
+  for (int hh = 0; hh < HG; ++hh) mx[hh] = warp_max(mx[hh]);
+  __syncthreads();
+  if (l == 0) {
+#pragma unroll
+    for (int hh = 0; hh < HG; ++hh) red[w * HG + hh] = mx[hh];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int hh = 0; hh < HG; ++hh) mx[hh] = warp_max(l < nw ? red[l * HG + hh] : -INFINITY);
+  float sum[HG] = {};
+  for (int jj = threadIdx.x; jj < n; jj += blockDim.x) {
+    float4 v = *reinterpret_cast<const float4*>(sc + jj * HG);
+    v.x = expf(v.x - mx[0]); v.y = expf(v.y - mx[1]); v.z = expf(v.z - mx[2]); v.w = expf(v.w - mx[3]);
+    *reinterpret_cast<float4*>(sc + jj * HG) = v;
+    sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
+  }
+#pragma unroll
+  for (int hh = 0; hh < HG; ++hh) sum[hh] = warp_sum(sum[hh]);
+  __syncthreads();  // every thread has read the maxima
+  if (l == 0) {
+#pragma unroll
+    for (int hh = 0; hh < HG; ++hh) red[w * HG + hh] = sum[hh];
+  }
+  __syncthreads();  // also publishes the exponentials in sc[]
+#pragma unroll
+  for (int hh = 0; hh < HG; ++hh) inv[hh] = 1.f / (warp_sum(l < nw ? red[l * HG + hh] : 0.f) + expf(sink[hh] - mx[hh]));
+  if (sizeof(CT) == 2 && (D & 7) == 0 && (a.R & 7) == 0 && a.R / 8 <= (int)blockDim.x) {
+    // bf16 rows: a thread owns 8 consecutive latent entries (one 16-byte load per key), the block's threads form G groups
+    // that take every G-th key, so many loads are in flight per SM; groups are summed in group order, one head at a time
+    const int RC = a.R / 8, G = blockDim.x / RC, g = threadIdx.x / RC, c = threadIdx.x % RC;
+    const bf16* base = reinterpret_cast<const bf16*>(cache) + c * 8;
+    float acc[HG][8] = {};
+    auto add_key = [&](const uint4& u, const float4& p) {
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+      const float pw[HG] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(p2[e]);
+#pragma unroll
+        for (int hh = 0; hh < HG; ++hh) {
+          acc[hh][2 * e] = fmaf(pw[hh], f.x, acc[hh][2 * e]);
+          acc[hh][2 * e + 1] = fmaf(pw[hh], f.y, acc[hh][2 * e + 1]);
+        }
+      }
+    };
+    if (g < G) {
+      int jj = g;
+      for (; jj + G < n; jj += 2 * G) {  // two rows in flight; added in key order
+        const uint4 u0 = *reinterpret_cast<const uint4*>(base + (size_t)rowoff[jj] * D);
+        const uint4 u1 = *reinterpret_cast<const uint4*>(base + (size_t)rowoff[jj + G] * D);
+        add_key(u0, *reinterpret_cast<const float4*>(sc + jj * HG));
+        add_key(u1, *reinterpret_cast<const float4*>(sc + (jj + G) * HG));
+      }
+      if (jj < n) add_key(*reinterpret_cast<const uint4*>(base + (size_t)rowoff[jj] * D), *reinterpret_cast<const float4*>(sc + jj * HG));
+    }
+#pragma unroll
+    for (int hh = 0; hh < HG; ++hh) {
+      __syncthreads();
+      if (g < G) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) part[g * a.R + c * 8 + e] = acc[hh][e];
+      }
+      __syncthreads();
+      if (hh < nh)
+        for (int r = threadIdx.x; r < a.R; r += blockDim.x) {
+          float tot = 0.f;
+          for (int gg = 0; gg < G; ++gg) tot += part[gg * a.R + r];
+          a.ctx[(size_t)t * a.ldc + (size_t)(h0 + hh) * a.R + r] = tot * inv[hh];
+        }
+    }
+    return;
+  }
   const int Rp = (a.R + 31) / 32 * 32;
   const int G = max(1, (int)blockDim.x / Rp);
   for (int r0 = 0; r0 < a.R; r0 += blockDim.x) {  // one pass unless the latent is wider than the block
     const int g = (G > 1) ? threadIdx.x / Rp : 0, r = r0 + ((G > 1) ? threadIdx.x % Rp : threadIdx.x);
-    float acc = 0.f;
+    float acc[HG] = {};
     if (g < G && r < a.R) {
       const CT* col = cache + r;
       int jj = g;
-      for (; jj + 3 * G < n; jj += 4 * G) {  // four independent loads in flight; the sum keeps key order
+      for (; jj + G < n; jj += 2 * G) {  // two independent loads in flight; the sum keeps key order
         const float c0 = ldf<CT>(col, (size_t)rowoff[jj] * D), c1 = ldf<CT>(col, (size_t)rowoff[jj + G] * D);
-        const float c2 = ldf<CT>(col, (size_t)rowoff[jj + 2 * G] * D), c3 = ldf<CT>(col, (size_t)rowoff[jj + 3 * G] * D);
-        acc = fmaf(sc[jj], c0, acc);
-        acc = fmaf(sc[jj + G], c1, acc);
-        acc = fmaf(sc[jj + 2 * G], c2, acc);
-        acc = fmaf(sc[jj + 3 * G], c3, acc);
+        const float4 p0 = *reinterpret_cast<const float4*>(sc + jj * HG), p1 = *reinterpret_cast<const float4*>(sc + (jj + G) * HG);
+        acc[0] = fmaf(p0.x, c0, acc[0]); acc[1] = fmaf(p0.y, c0, acc[1]); acc[2] = fmaf(p0.z, c0, acc[2]); acc[3] = fmaf(p0.w, c0, acc[3]);
+        acc[0] = fmaf(p1.x, c1, acc[0]); acc[1] = fmaf(p1.y, c1, acc[1]); acc[2] = fmaf(p1.z, c1, acc[2]); acc[3] = fmaf(p1.w, c1, acc[3]);
       }
-      for (; jj < n; jj += G) acc = fmaf(sc[jj], ldf<CT>(col, (size_t)rowoff[jj] * D), acc);
+      for (; jj < n; jj += G) {
+        const float c0 = ldf<CT>(col, (size_t)rowoff[jj] * D);
+        const float4 p0 = *reinterpret_cast<const float4*>(sc + jj * HG);
+        acc[0] = fmaf(p0.x, c0, acc[0]); acc[1] = fmaf(p0.y, c0, acc[1]); acc[2] = fmaf(p0.z, c0, acc[2]); acc[3] = fmaf(p0.w, c0, acc[3]);
+      }
     }
     if (G > 1) {
       __syncthreads();
-      part[threadIdx.x] = acc;
+#pragma unroll
+      for (int hh = 0; hh < HG; ++hh) part[threadIdx.x * HG + hh] = acc[hh];
       __syncthreads();
       if (threadIdx.x < a.R) {
-        float tot = 0.f;
-        for (int gg = 0; gg < G; ++gg) tot += part[gg * Rp + threadIdx.x];
-        a.ctx[(size_t)t * a.ldc + (size_t)h * a.R + threadIdx.x] = tot * inv;
+#pragma unroll
+        for (int hh = 0; hh < HG; ++hh) {
+          float tot = 0.f;
+          for (int gg = 0; gg < G; ++gg) tot += part[(gg * Rp + threadIdx.x) * HG + hh];
+          if (hh < nh) a.ctx[(size_t)t * a.ldc + (size_t)(h0 + hh) * a.R + threadIdx.x] = tot * inv[hh];
+        }
       }
     } else if (r < a.R) {
-      a.ctx[(size_t)t * a.ldc + (size_t)h * a.R + r] = acc * inv;
+#pragma unroll
+      for (int hh = 0; hh < HG; ++hh)
+        if (hh < nh) a.ctx[(size_t)t * a.ldc + (size_t)(h0 + hh) * a.R + r] = acc[hh] * inv[hh];
     }
   }
 }
@@ -781,9 +882,9 @@ cudaError_t latent_q_rope(cudaStream_t s, const float* q, long ldq, float* qabs,
 
 cudaError_t latent_attn(cudaStream_t s, const LatentAttnArgs& a) {
   if (a.T <= 0) return cudaSuccess;
-  const size_t smem = (size_t)((a.R + a.Dr + 3) / 4 * 4 + 2 * a.window + kLatThreads + 32) * 4;
+  const size_t smem = (size_t)(kLatHG * ((a.R + a.Dr + 3) / 4 * 4) + (kLatHG + 1) * a.window + 8 * kLatThreads + 32 * kLatHG) * 4;
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
-  dim3 grid(a.T, a.H);
+  dim3 grid(a.T, (a.H + kLatHG - 1) / kLatHG);
   if (a.f32) latent_attn_kernel<float, float><<<grid, kLatThreads, smem, s>>>(a);
   else latent_attn_kernel<bf16, bf16><<<grid, kLatThreads, smem, s>>>(a);
   return KERR();
