@@ -61,6 +61,12 @@ __global__ void fill_uniform_kernel(T* p, size_t n, uint64_t seed, float amp, fl
 int Engine::load_begin_stack(const hb_stack_desc& sd, const hb_layer_desc* layers) {
   std::lock_guard<std::mutex> g(gpu_mu_);
   if (loaded_ || load_open_) return fail(HB_ERR_STATE, "model already loaded on this engine");
+  if (!layers || sd.n_layers <= 0) return fail(HB_ERR_INVALID, "unsupported model description: no layer list");
+  // no position reaches max_ctx, so a longer window sees what a window of max_ctx sees: size the kernels for the shorter one
+  std::vector<hb_layer_desc> lv(layers, layers + sd.n_layers);
+  for (hb_layer_desc& l : lv)
+    if (l.mixer == HB_MIXER_LATENT && l.window > cfg_.max_ctx) l.window = cfg_.max_ctx;
+  layers = lv.data();
   const std::string why = validate_stack(sd, layers);
   if (!why.empty()) return fail(HB_ERR_INVALID, "unsupported model description: " + why);
   CU(cudaSetDevice(cfg_.device));

@@ -304,6 +304,18 @@ def test_tensor_core_head_products_and_long_windows():
             assert row_err(replay(e, toks, [290, 300, 70, 38]), want).max() < TOL[f32]
 
 
+def test_window_longer_than_the_context():
+    # a window no sequence can fill is full causal attention: nothing may be sized by the configured number
+    cfg = ref.random_config(order=("latent_attention", "gla"), lat=dict(window=1 << 20))
+    sd = ref.random_state_dict(cfg, seed=43)
+    toks = tokens(9, 120, cfg["vocab"])
+    want = ref.RisepelOracle(cfg, sd).forward(toks)
+    for f32 in (1, 0):
+        with make_engine(cfg, sd, f32, ctx=128) as e:
+            assert row_err(replay(e, toks, [len(toks)]), want).max() < TOL[f32]
+            assert row_err(replay(e, toks, [70, 2, 30]), want).max() < TOL[f32]
+
+
 def test_runtime_serves_a_checkpoint_folder(tmp_path):
     import json
     from helix_b200.runtime import B200Runtime, B200RuntimeParams
