@@ -31,12 +31,16 @@ class LayerDescC(C.Structure):
     _fields_ = [("mixer", C.c_int32), ("heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("tau", C.c_float),
                 ("decay_rank", C.c_int32), ("q_rank", C.c_int32), ("kv_rank", C.c_int32), ("rot_dim", C.c_int32),
                 ("rope_dims", C.c_int32), ("window", C.c_int32), ("kv_from", C.c_int32), ("rope_base", C.c_float),
-                ("scale", C.c_float), ("ff", C.c_int32), ("ff_limit", C.c_float), ("reserved", C.c_int32 * 4)]
+                ("scale", C.c_float), ("ff", C.c_int32), ("ff_limit", C.c_float), ("kv_heads", C.c_int32), ("mask", C.c_int32),
+                ("attn_flags", C.c_int32), ("rope_pairing", C.c_int32), ("rope_factor", C.c_float), ("rope_low", C.c_float),
+                ("rope_high", C.c_float), ("rope_original", C.c_int32), ("ff_kind", C.c_int32), ("experts", C.c_int32),
+                ("identity_experts", C.c_int32), ("top_k", C.c_int32), ("reserved", C.c_int32 * 4)]
 
 
 class StackDescC(C.Structure):
     _fields_ = [("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("compute_f32", C.c_int32),
-                ("norm_eps", C.c_float), ("resid_alpha", C.c_float), ("logit_softcap", C.c_float), ("reserved", C.c_int32 * 5)]
+                ("norm_eps", C.c_float), ("resid_alpha", C.c_float), ("logit_softcap", C.c_float), ("norm_place", C.c_int32),
+                ("embed_norm", C.c_int32), ("plain_gains", C.c_int32), ("reserved", C.c_int32 * 2)]
 
 
 class SeqFeedC(C.Structure):

@@ -196,6 +196,11 @@ class Engine {
     float* S = nullptr;
     int att_qb = 0;       // tokens per query block
     size_t att_rows = 0, att_keys = 0;  // capacity: score rows (tokens x heads) and key columns of one block
+    // mixture of experts: router logits [T][ldz], chosen outputs and their weights [T][top_k], expert outputs [(T, top_k)][W]
+    float *moe_z = nullptr, *moe_w = nullptr, *moe_y = nullptr;
+    int32_t* moe_ids = nullptr;
+    int ldz = 0;
+    std::vector<const double*> freqs;  // per layer: rotation frequencies of a grouped-query layer (device), else null
   } sk_{};
   struct StepEntry { int t0, first, n; };  // host copy of the step's entries: first packed row, first position, tokens
   std::vector<StepEntry> step_entries_;

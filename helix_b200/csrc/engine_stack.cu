@@ -64,11 +64,18 @@ int Engine::load_begin_stack(const hb_stack_desc& sd, const hb_layer_desc* layer
   if (!layers || sd.n_layers <= 0) return fail(HB_ERR_INVALID, "unsupported model description: no layer list");
   // no position reaches max_ctx, so a longer window sees what a window of max_ctx sees: size the kernels for the shorter one
   std::vector<hb_layer_desc> lv(layers, layers + sd.n_layers);
-  for (hb_layer_desc& l : lv)
+  for (hb_layer_desc& l : lv) {
     if (l.mixer == HB_MIXER_LATENT && l.window > cfg_.max_ctx) l.window = cfg_.max_ctx;
+    if (l.mixer == HB_MIXER_GQA) {  // a block or window that no sequence outgrows is the causal mask
+      if (l.mask == HB_MASK_CAUSAL || l.window >= cfg_.max_ctx) { l.mask = HB_MASK_WINDOW; l.window = cfg_.max_ctx; }
+    }
+  }
   layers = lv.data();
   const std::string why = validate_stack(sd, layers);
   if (!why.empty()) return fail(HB_ERR_INVALID, "unsupported model description: " + why);
+  for (const hb_layer_desc& l : lv)
+    if (l.mixer == HB_MIXER_GQA && gqa_attn_smem(l.dim, l.vdim, l.window) > 200 * 1024)
+      return fail(HB_ERR_INVALID, "unsupported model description: the keys one position sees exceed the attention kernel's shared memory");
   CU(cudaSetDevice(cfg_.device));
   size_t free_b = 0, total_b = 0;
   CU(cudaMemGetInfo(&free_b, &total_b));
@@ -164,26 +171,46 @@ static bool stack_att_caps(const Model& m, int* qb, size_t* rows, size_t* keys, 
   return true;
 }
 
+// widest buffers any layer needs (columns per token)
+struct StackDims {
+  int n1 = 0, n2 = 0, q = 0, qa = 0, cx = 0, mo = 0;
+  int moe_r = 0, moe_top = 0, rope_half = 0;
+};
+static StackDims stack_dims(const Model& m) {
+  StackDims d;
+  for (int i = 0; i < m.sd.n_layers; ++i) {
+    const hb_layer_desc& l = m.sl[i];
+    d.n1 = std::max(d.n1, std::max(m.sw[i].n_in, 2 * l.ff));
+    d.mo = std::max(d.mo, std::max(l.heads * l.vdim, l.ff));
+    if (l.mixer == HB_MIXER_GLA) {
+      d.n2 = std::max(d.n2, l.heads * l.dim);
+      d.cx = std::max(d.cx, l.heads * l.vdim);
+    } else if (l.mixer == HB_MIXER_GQA) {
+      d.n2 = std::max(d.n2, l.heads * l.dim);
+      d.rope_half += l.rope_dims / 2;
+    } else {
+      d.n2 = std::max(d.n2, l.heads * (l.dim + l.rot_dim));
+      d.q = std::max(d.q, l.q_rank);
+      d.qa = std::max(d.qa, l.heads * (l.kv_rank + l.rot_dim));
+      d.cx = std::max(d.cx, std::max(l.heads * l.kv_rank, l.heads * l.vdim));
+    }
+    if (l.ff > 0 && l.ff_kind == HB_FF_MOE) {
+      d.moe_r = std::max(d.moe_r, l.experts + l.identity_experts);
+      d.moe_top = std::max(d.moe_top, l.top_k);
+    }
+  }
+  return d;
+}
+
 size_t Engine::workspace_bytes_stack() const {
   const hb_stack_desc& sd = model_.sd;
   const size_t T = t_cap_, W = sd.width;
-  int n1 = 0, n2 = 0, q = 0, qa = 0, cx = 0, mo = 0;
-  for (int i = 0; i < sd.n_layers; ++i) {
-    const hb_layer_desc& l = model_.sl[i];
-    n1 = std::max(n1, model_.sw[i].n_in);
-    n1 = std::max(n1, 2 * l.ff);
-    mo = std::max(mo, std::max(l.heads * l.vdim, l.ff));
-    if (l.mixer == HB_MIXER_GLA) {
-      n2 = std::max(n2, l.heads * l.dim);
-      cx = std::max(cx, l.heads * l.vdim);
-    } else {
-      n2 = std::max(n2, l.heads * (l.dim + l.rot_dim));
-      q = std::max(q, l.q_rank);
-      qa = std::max(qa, l.heads * (l.kv_rank + l.rot_dim));
-      cx = std::max(cx, std::max(l.heads * l.kv_rank, l.heads * l.vdim));
-    }
-  }
+  const StackDims dm = stack_dims(model_);
+  const int n1 = dm.n1, n2 = dm.n2, q = dm.q, qa = dm.qa, cx = dm.cx, mo = dm.mo;
   size_t b = 0;
+  b += al256((size_t)std::max(dm.rope_half, 1) * 8);
+  if (dm.moe_r > 0)
+    b += al256(T * (size_t)up8(dm.moe_r) * 4) + 2 * al256(T * (size_t)dm.moe_top * 4) + al256(T * (size_t)dm.moe_top * W * 4);
   b += 2 * al256(T * W * 4) + al256(T * W * 2);                       // x, y, x16
   b += al256(T * (size_t)up8(n1) * 4) + al256(T * (size_t)up8(n2) * 4);  // p1, p2
   b += al256(T * (size_t)up8(q) * 4) + al256(T * (size_t)up8(q) * 2);     // cq, cq16
@@ -206,6 +233,8 @@ int Engine::alloc_runtime_stack() {
   const hb_stack_desc& sd = model_.sd;
   cfg_.enable_prefix_cache = 0;  // a page of latent rows does not carry the recurrent layers' state of its prefix
   CU(stack_ops_init());
+  CU(stack_gqa_init());
+  CU(stack_moe_init());
   if (!sd.compute_f32) {  // stream-K plans allocate on first use of a shape: make them now, not inside a graph capture
     SmLimitScope sm_scope(cfg_.sm_budget);
     SkinnyPlan pl{};
@@ -233,20 +262,27 @@ int Engine::alloc_runtime_stack() {
     return r;
   };
   const size_t T = t_cap_, W = sd.width;
-  int n1 = 0, n2 = 0, q = 0, qa = 0, cx = 0, mo = 0;
-  for (int i = 0; i < sd.n_layers; ++i) {
-    const hb_layer_desc& l = model_.sl[i];
-    n1 = std::max(n1, std::max(model_.sw[i].n_in, 2 * l.ff));
-    mo = std::max(mo, std::max(l.heads * l.vdim, l.ff));
-    if (l.mixer == HB_MIXER_GLA) {
-      n2 = std::max(n2, l.heads * l.dim);
-      cx = std::max(cx, l.heads * l.vdim);
-    } else {
-      n2 = std::max(n2, l.heads * (l.dim + l.rot_dim));
-      q = std::max(q, l.q_rank);
-      qa = std::max(qa, l.heads * (l.kv_rank + l.rot_dim));
-      cx = std::max(cx, std::max(l.heads * l.kv_rank, l.heads * l.vdim));
+  const StackDims dm = stack_dims(model_);
+  const int n1 = dm.n1, n2 = dm.n2, q = dm.q, qa = dm.qa, cx = dm.cx, mo = dm.mo;
+  {  // rotation frequencies of the grouped-query layers (double precision, formed on the host)
+    double* fq = (double*)take((size_t)std::max(dm.rope_half, 1) * 8);
+    sk_.freqs.assign(sd.n_layers, nullptr);
+    size_t at = 0;
+    for (int i = 0; i < sd.n_layers; ++i) {
+      const hb_layer_desc& l = model_.sl[i];
+      if (l.mixer != HB_MIXER_GQA || l.rope_dims <= 0) continue;
+      const std::vector<double> f = stack_rope_freqs(l);
+      CU(cudaMemcpy(fq + at, f.data(), f.size() * 8, cudaMemcpyHostToDevice));
+      sk_.freqs[i] = fq + at;
+      at += f.size();
     }
+  }
+  if (dm.moe_r > 0) {
+    sk_.ldz = up8(dm.moe_r);
+    sk_.moe_z = (float*)take(T * (size_t)sk_.ldz * 4);
+    sk_.moe_ids = (int32_t*)take(T * (size_t)dm.moe_top * 4);
+    sk_.moe_w = (float*)take(T * (size_t)dm.moe_top * 4);
+    sk_.moe_y = (float*)take(T * (size_t)dm.moe_top * W * 4);
   }
   sk_.ld1 = up8(n1); sk_.ld2 = up8(n2); sk_.ldcq = up8(q); sk_.ldqa = up8(qa); sk_.ldctx = up8(cx); sk_.ldmo = up8(mo);
   sk_.x = (float*)take(T * W * 4);
@@ -394,7 +430,14 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
   bf16* mo16 = f32 ? nullptr : k.mo16;
   const double rowb = 4.0 * T * W;
 
+  const float goff = sd.plain_gains ? 0.f : 1.f;  // stored norm gains are offsets from one unless plain
+  // the residual step: the norm covers the sum (post-norm stream) or the sublayer's output alone
+  auto resid = [&](const void* bias, const void* gain) -> cudaError_t {
+    if (sd.norm_place == HB_NORM_OF_OUTPUT) return resid_add_normed(stream_, k.x, x16, k.y, W, bias, gain, f32, goff, sd.norm_eps, T, W);
+    return resid_postnorm(stream_, k.x, x16, k.y, W, bias, gain, f32, sd.resid_alpha, goff, sd.norm_eps, T, W);
+  };
   SPAN(3, rowb, embed_rows_f32(stream_, tokens, model_.s_embed, f32, k.x, x16, T, W));
+  if (sd.embed_norm) SPAN(3, 2 * rowb, norm_rows_f32(stream_, k.x, nullptr, model_.s_embed_norm, f32, goff, sd.norm_eps, k.x, x16, T, W));
   for (int i = 0; i < sd.n_layers; ++i) {
     const hb_layer_desc& l = model_.sl[i];
     const StackLayerW& w = model_.sw[i];
@@ -417,6 +460,29 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       a.q_scale = 1.0f / sqrtf((float)Dk);
       SPAN(6, 4.0 * T * H * Dk * Dv, gla_recurrence(stream_, a));
       SPAN(3, 12.0 * T * H * Dv, headnorm_silu_gate(stream_, k.ctx, k.ldctx, k.p1 + w.off_g, k.ld1, w.hnorm, f32, sd.norm_eps, k.mo, mo16, T, H, Dv));
+    } else if (l.mixer == HB_MIXER_GQA) {
+      const int G = l.kv_heads;
+      void* kplane = (uint8_t*)kv_ + plane_off_[w.cache_plane];
+      void* vplane = (uint8_t*)kv_ + plane_off_[w.cache_plane_v];
+      GqaPrepArgs pa{};
+      pa.p = k.p1; pa.ldp = k.ld1; pa.q_off = w.off_q; pa.k_off = w.off_k; pa.v_off = w.off_v;
+      pa.q = k.p2; pa.ldq = H * Dk; pa.q_b16 = nullptr;
+      pa.k_cache = kplane; pa.v_cache = vplane; pa.f32 = f32;
+      pa.slots = slots; pa.positions = positions;
+      pa.freqs = k.freqs[i]; pa.rope_dims = l.rope_dims; pa.pairing = l.rope_pairing;
+      pa.H = H; pa.G = G; pa.D = Dk; pa.Dv = Dv; pa.page_size = page_;
+      pa.unit_norm = (l.attn_flags & HB_ATTN_QK_UNIT_NORM) != 0; pa.eps = sd.norm_eps; pa.T = T;
+      SPAN(3, 8.0 * T * (H + 2 * G) * Dk, gqa_prep(stream_, pa));
+      GqaAttnArgs aa{};
+      aa.q = k.p2; aa.ldq = H * Dk;
+      aa.k_cache = kplane; aa.v_cache = vplane; aa.f32 = f32;
+      aa.page_table = pt; aa.max_pages = max_pages_per_seq_; aa.page_size = page_;
+      aa.positions = positions; aa.seq_of = seqof;
+      aa.gate = (l.attn_flags & HB_ATTN_HEAD_GATE) ? k.p1 + w.off_g : nullptr; aa.ldg = k.ld1;
+      aa.out = k.mo; aa.ldo = H * Dv; aa.out_b16 = mo16;
+      aa.T = T; aa.H = H; aa.G = G; aa.D = Dk; aa.Dv = Dv; aa.mask = l.mask; aa.window = l.window;
+      aa.unit_sink = (l.attn_flags & HB_ATTN_UNIT_SINK) != 0; aa.scale = l.scale;
+      SPAN(7, 2.0 * T * H * (double)std::min(l.window, cfg_.max_ctx) * (Dk + Dv), gqa_attn(stream_, aa));
     } else {
       const int R = l.kv_rank, Dr = l.rot_dim, Q = l.q_rank;
       uint8_t* plane = (uint8_t*)kv_ + plane_off_[w.cache_plane];
@@ -512,8 +578,25 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
     }
     rc = stack_gemm(k.mo, mo16, H * Dv, w.wo, W, H * Dv, k.y, W, T);
     if (rc != HB_OK) return rc;
-    SPAN(3, 3 * rowb, resid_postnorm(stream_, k.x, x16, k.y, W, nullptr, w.norm1, f32, sd.resid_alpha, 1.f, sd.norm_eps, T, W));
-    if (l.ff > 0) {
+    SPAN(3, 3 * rowb, resid(nullptr, w.norm1));
+    if (l.ff > 0 && l.ff_kind == HB_FF_MOE) {
+      // router in fp32 on the stream itself; experts per (token, choice); identity outputs and weights in the combination
+      const int E = l.experts, R = l.experts + l.identity_experts, F = l.ff;
+      GemmRtArgs g{k.x, W, 0, w.router, W, 1, 0, k.moe_z, k.ldz, 0, nullptr, T, R, W, 1, f32};
+      SPAN(5, 2.0 * T * R * W, gemm_rt(stream_, g));
+      SPAN(3, 8.0 * T * R, moe_route(stream_, k.moe_z, k.ldz, w.correction, f32, R, l.top_k, k.moe_ids, k.moe_w, T));
+      SPAN(5, 6.0 * T * l.top_k * F * W, moe_expert_rows(stream_, k.x, x16, w.w_gu, w.w_down, f32, k.moe_ids, l.top_k, E, F, W, k.moe_y, T));
+      SPAN(3, 4.0 * T * (l.top_k + 2) * W, moe_combine(stream_, k.x, k.moe_y, k.moe_ids, k.moe_w, l.top_k, E, k.y, T, W));
+      SPAN(3, 3 * rowb, resid(nullptr, w.norm2));
+    } else if (l.ff > 0 && l.ff_kind == HB_FF_GELU_TANH) {
+      const int F = l.ff;
+      rc = stack_gemm(k.x, x16, W, w.w_gu, 2 * F, W, k.p1, k.ld1, T);
+      if (rc != HB_OK) return rc;
+      SPAN(3, 12.0 * T * F, gated_unit(stream_, k.p1, k.ld1, GLU_GELU_TANH, k.mo, mo16, T, F));
+      rc = stack_gemm(k.mo, mo16, F, w.w_down, W, F, k.y, W, T);
+      if (rc != HB_OK) return rc;
+      SPAN(3, 3 * rowb, resid(nullptr, w.norm2));
+    } else if (l.ff > 0) {
       const int F = l.ff;
       rc = stack_gemm(k.x, x16, W, w.w_gu, 2 * F, W, k.p1, k.ld1, T);
       if (rc != HB_OK) return rc;
@@ -521,7 +604,7 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       SPAN(3, 12.0 * T * F, clamped_glu(stream_, k.p1, k.ld1, w.b_gu, bu, f32, l.ff_limit, 1.702f, k.mo, mo16, T, F));
       rc = stack_gemm(k.mo, mo16, F, w.w_down, W, F, k.y, W, T);
       if (rc != HB_OK) return rc;
-      SPAN(3, 3 * rowb, resid_postnorm(stream_, k.x, x16, k.y, W, w.b_down, w.norm2, f32, sd.resid_alpha, 1.f, sd.norm_eps, T, W));
+      SPAN(3, 3 * rowb, resid(w.b_down, w.norm2));
     }
   }
   // logits: final norm -> head -> soft cap, for the entries' last rows (sampling) and for the rows asked for
@@ -530,7 +613,7 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       const int m = std::min(t_cap_, n - r0);
       const int32_t* idx = rows ? rows + r0 : nullptr;
       const float* src = rows ? k.x : k.x + (size_t)r0 * W;
-      LAUNCH(norm_rows_f32(stream_, src, idx, model_.s_final_norm, f32, 1.f, sd.norm_eps, k.y, x16, m, W));
+      LAUNCH(norm_rows_f32(stream_, src, idx, model_.s_final_norm, f32, goff, sd.norm_eps, k.y, x16, m, W));
       int rc = stack_gemm(k.y, x16, W, model_.s_head, V, W, out + (size_t)r0 * V, V, m);
       if (rc != HB_OK) return rc;
     }

@@ -262,7 +262,10 @@ cudaError_t embed_rows_f32(cudaStream_t s, const int32_t* tokens, const void* ta
 // Post-norm residual step: x[t] <- rmsnorm(alpha * x[t] + y[t] (+ bias)) * (gain_offset + w);  rows of y have stride ldy
 cudaError_t resid_postnorm(cudaStream_t s, float* x, bf16* x_b16, const float* y, long ldy, const void* bias, const void* w,
                            bool f32, float alpha, float gain_offset, float eps, int T, int W);
-// out[r] = rmsnorm(x[row_index ? row_index[r] : r]) * (gain_offset + w)
+// Residual step with the norm on the sublayer's output only: x[t] <- x[t] + rmsnorm(y[t] (+ bias)) * (gain_offset + w)
+cudaError_t resid_add_normed(cudaStream_t s, float* x, bf16* x_b16, const float* y, long ldy, const void* bias, const void* w,
+                             bool f32, float gain_offset, float eps, int T, int W);
+// out[r] = rmsnorm(x[row_index ? row_index[r] : r]) * (gain_offset + w)   (out may be x itself when row_index is null)
 cudaError_t norm_rows_f32(cudaStream_t s, const float* x, const int32_t* row_index, const void* w, bool f32, float gain_offset,
                           float eps, float* out, bf16* out_b16, int rows, int W);
 // logits <- cap * tanh(logits / cap), in place on [rows, V]
@@ -340,5 +343,58 @@ cudaError_t transpose_heads_bf16(cudaStream_t s, const bf16* src, bf16* dst, int
 cudaError_t sigmoid_gate(cudaStream_t s, const float* o, long ldo, const float* g, long ldg, float* out, bf16* out_b16, int T, int N);
 // f32 -> bf16 copy of a [T, N] block (row strides lds / ldd)
 cudaError_t to_bf16_rows(cudaStream_t s, const float* src, long lds, bf16* dst, long ldd, int T, int N);
+
+// ---- grouped-query attention over per-head key / value planes [page][kv_head][page_size][D | Dv] (stack_gqa.cu).
+cudaError_t stack_gqa_init();
+enum StackMask : int { MASK_WINDOW = 0, MASK_CHUNK = 1, MASK_CAUSAL = 2 };  // == hb_mask
+// From the fused projection p[t] = [q (H*D) | k (G*D) | v (G*Dv, or the k columns again) | ...]: the first rope_dims entries of
+// every q and k head turn by pos * freqs[i] (pairing 1: entries (2i, 2i+1); 0: (i, i + rope_dims/2); angles in double
+// precision), then q and k are divided by their root mean square over D when unit_norm.  q goes to q[t, h*D..] (+ bf16 copy),
+// k and the UNTOUCHED v columns to the cache rows of slots[t] (slot < 0: no cache write).
+struct GqaPrepArgs {
+  const float* p; long ldp; int q_off, k_off, v_off;
+  float* q; long ldq; bf16* q_b16;
+  void* k_cache; void* v_cache; bool f32;
+  const int32_t* slots; const int32_t* positions;
+  const double* freqs; int rope_dims, pairing;
+  int H, G, D, Dv, page_size;
+  bool unit_norm; float eps;
+  int T;
+};
+cudaError_t gqa_prep(cudaStream_t s, const GqaPrepArgs& a);
+// out[t, h, :] = gate_h * sum_j p_j v_j over the keys position pos_t sees, p_j = exp(s_j) / (sum_i exp(s_i) + sink),
+// s_j = scale * q[t, h] . k_j (head h reads kv head h / (H / G)).  Visible keys: mask 0 (window) pos - window < j <= pos;
+// 1 (chunk) j <= pos in the block of `window` positions that holds pos; 2 (causal) j <= pos.  sink = 1 when unit_sink
+// (a key with score 0 and no value), else 0.  gate_h = sigmoid(gate[t, h]) or 1 when gate is null.
+struct GqaAttnArgs {
+  const float* q; long ldq;
+  const void* k_cache; const void* v_cache; bool f32;
+  const int32_t* page_table; int max_pages, page_size;
+  const int32_t* positions; const int32_t* seq_of;
+  const float* gate; long ldg;
+  float* out; long ldo; bf16* out_b16;
+  int T, H, G, D, Dv, mask, window;
+  bool unit_sink; float scale;
+};
+cudaError_t gqa_attn(cudaStream_t s, const GqaAttnArgs& a);
+size_t gqa_attn_smem(int D, int Dv, int max_keys);  // dynamic shared memory the kernel needs to see max_keys keys
+
+// ---- gated feed-forward units and mixtures of experts (stack_moe.cu).
+cudaError_t stack_moe_init();
+enum GluAct : int { GLU_SILU = 0, GLU_GELU_TANH = 1 };
+// out[t, j] = act(gu[t, j]) * gu[t, F + j]   (row stride ldg)
+cudaError_t gated_unit(cudaStream_t s, const float* gu, long ldg, int act, float* out, bf16* out_b16, int T, int F);
+// Router: scores = softmax(z[t, :R]) in fp32; the top_k largest of (score + correction) are chosen, lowest index first among
+// equals; ids[t, k] = chosen output, wts[t, k] = its score (not renormalised)
+cudaError_t moe_route(cudaStream_t s, const float* z, long ldz, const void* correction, bool f32, int R, int top_k, int32_t* ids,
+                      float* wts, int T);
+// One block per (token, choice): y[(t, k), :] = down_e(silu(gate_e x_t) * (up_e x_t)) for ids[t, k] = e < E (rows of choices
+// that name an identity output are left alone).  x_b16 != null: the unit reads the bf16 copy of x and rounds its inner
+// activation to bf16, as the tensor-core path does.  w_gu: [E][2F][W] ([gate | up] rows), w_down: [E][W][F].
+cudaError_t moe_expert_rows(cudaStream_t s, const float* x, const bf16* x_b16, const void* w_gu, const void* w_down, bool f32,
+                            const int32_t* ids, int top_k, int E, int F, int W, float* y, int T);
+// out[t, :] = sum_k wts[t, k] * (ids[t, k] < E ? y[(t, k), :] : x[t, :]), k in order
+cudaError_t moe_combine(cudaStream_t s, const float* x, const float* y, const int32_t* ids, const float* wts, int top_k, int E,
+                        float* out, int T, int W);
 
 }  // namespace hb

@@ -184,12 +184,52 @@ std::string validate_stack(const hb_stack_desc& d, const hb_layer_desc* L) {
         if (s.mixer != HB_MIXER_LATENT || s.kv_from >= 0) return "kv_from must name a latent layer with its own cache rows" + at;
         if (s.kv_rank != l.kv_rank || s.rot_dim != l.rot_dim) return "kv_from layer has a different latent row" + at;
       }
+    } else if (l.mixer == HB_MIXER_GQA) {
+      if (l.kv_heads <= 0 || l.heads % l.kv_heads) return "heads must be a multiple of kv_heads" + at;
+      if ((l.attn_flags & HB_ATTN_V_IS_K) && l.vdim != l.dim) return "values that are the keys need vdim == dim" + at;
+      if (l.rope_dims < 0 || l.rope_dims % 2 || l.rope_dims > l.dim) return "rope_dims must be even and <= dim" + at;
+      if (l.rope_dims > 0 && !(l.rope_base > 0.f)) return "rope_base must be positive" + at;
+      if (l.rope_pairing != 0 && l.rope_pairing != 1) return "unknown rope_pairing" + at;
+      if (l.rope_factor > 0.f && (l.rope_original <= 0 || !(l.rope_high > l.rope_low))) return "rope scaling needs original > 0 and high > low" + at;
+      if (l.mask != HB_MASK_WINDOW && l.mask != HB_MASK_CHUNK && l.mask != HB_MASK_CAUSAL) return "unknown mask" + at;
+      if (l.mask != HB_MASK_CAUSAL && l.window <= 0) return "window / chunk size must be positive" + at;
+      if (l.dim > 512 || l.vdim > 512) return "head size > 512 unsupported" + at;
+      if (l.kv_from >= 0) return "kv_from is a latent-attention option" + at;
     } else {
       return "unknown mixer" + at;
     }
     if (l.ff < 0) return "negative ff" + at;
+    if (l.ff > 0) {
+      if (l.ff_kind == HB_FF_MOE) {
+        if (l.experts <= 0 || l.identity_experts < 0 || l.top_k <= 0 || l.top_k > l.experts + l.identity_experts) return "mixture-of-experts sizes" + at;
+        if (l.experts + l.identity_experts > 1024 || l.top_k > 32) return "more than 1024 router outputs or top_k > 32 unsupported" + at;
+      } else if (l.ff_kind != HB_FF_CLAMPED && l.ff_kind != HB_FF_GELU_TANH) {
+        return "unknown feed-forward kind" + at;
+      }
+    }
   }
+  if (d.norm_place != HB_NORM_OF_SUM && d.norm_place != HB_NORM_OF_OUTPUT) return "unknown norm_place";
   return "";
+}
+
+std::vector<double> stack_rope_freqs(const hb_layer_desc& l) {
+  const int half = l.rope_dims / 2;
+  std::vector<double> f(half);
+  for (int i = 0; i < half; ++i) f[i] = pow((double)l.rope_base, -2.0 * i / (double)l.rope_dims);
+  if (l.rope_factor > 0.f) {
+    const double factor = l.rope_factor, lo = l.rope_low, hi = l.rope_high, orig = l.rope_original;
+    for (int i = 0; i < half; ++i) {
+      const double wl = 2.0 * M_PI / f[i];
+      if (wl < orig / hi) continue;
+      if (wl > orig / lo) {
+        f[i] /= factor;
+      } else {
+        const double s = (orig / wl - lo) / (hi - lo);
+        f[i] = (1.0 - s) * f[i] / factor + s * f[i];
+      }
+    }
+  }
+  return f;
 }
 
 static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc* L, uint8_t* base) {
@@ -214,10 +254,14 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
     m->placements[name] = p;
   };
   const size_t W = d.width, V = d.vocab;
+  const float gain_fill = d.plain_gains ? 1.f : 0.f;  // neutral value of a stored residual-norm gain
   uint8_t* embed = take(V * W);
   put("embed", embed, 0, V, W);
+  uint8_t* embed_norm = d.embed_norm ? take(W) : nullptr;
+  if (d.embed_norm) put("embed.norm", embed_norm, 0, W, 1, true, gain_fill);
   if (m) {
     m->s_embed = embed;
+    m->s_embed_norm = embed_norm;
     m->sw.assign(d.n_layers, StackLayerW{});
     m->state_floats = 0;
     m->plane_row.clear();
@@ -231,7 +275,7 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
     StackLayerW w;
     const size_t H = l.heads, Dk = l.dim, Dv = l.vdim;
     uint8_t* n1 = take(W);
-    put(p + "norm1", n1, 0, W, 1, true, 0.f);
+    put(p + "norm1", n1, 0, W, 1, true, gain_fill);
     w.norm1 = n1;
     if (l.mixer == HB_MIXER_GLA) {
       const size_t r = l.decay_rank;
@@ -260,6 +304,29 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
       if (m) {
         w.state_off = m->state_floats;
         m->state_floats += H * Dk * Dv;
+      }
+    } else if (l.mixer == HB_MIXER_GQA) {
+      const size_t G = l.kv_heads;
+      const bool own_v = !(l.attn_flags & HB_ATTN_V_IS_K), gated = (l.attn_flags & HB_ATTN_HEAD_GATE) != 0;
+      w.off_q = 0;
+      w.off_k = (int)(H * Dk);
+      w.off_v = own_v ? (int)(H * Dk + G * Dk) : w.off_k;
+      w.off_g = (int)(H * Dk + G * Dk + (own_v ? G * Dv : 0));
+      w.n_in = w.off_g + (gated ? (int)H : 0);
+      uint8_t* in = take((size_t)w.n_in * W);
+      w.w_in = in;
+      put(p + "mix.q", in, w.off_q, H * Dk, W);
+      put(p + "mix.k", in, w.off_k, G * Dk, W);
+      if (own_v) put(p + "mix.v", in, w.off_v, G * Dv, W);
+      if (gated) put(p + "mix.g", in, w.off_g, H, W);
+      uint8_t* o = take(W * H * Dv);
+      put(p + "mix.o", o, 0, W, H * Dv);
+      w.wo = o;
+      w.cache_plane = planes++;
+      w.cache_plane_v = planes++;
+      if (m) {
+        m->plane_row.push_back((int)(G * Dk));
+        m->plane_row.push_back((int)(G * Dv));
       }
     } else {
       const size_t Q = l.q_rank, R = l.kv_rank, Dr = l.rot_dim;
@@ -298,14 +365,41 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
       }
       w.cache_plane = plane_of[i];
     }
-    if (l.ff > 0) {
+    if (l.ff > 0 && l.ff_kind == HB_FF_MOE) {
+      const size_t Fn = l.ff, E = l.experts, R = (size_t)l.experts + l.identity_experts;
+      uint8_t* n2 = take(W);
+      uint8_t* router = take(R * W);
+      uint8_t* corr = take(R);
+      uint8_t* gu = take(E * 2 * Fn * W);
+      uint8_t* dn = take(E * W * Fn);
+      put(p + "norm2", n2, 0, W, 1, true, gain_fill);
+      put(p + "mlp.router", router, 0, R, W);
+      put(p + "mlp.correction", corr, 0, R, 1, false, 1.f, true);
+      for (size_t e = 0; e < E; ++e) {
+        const std::string pe = p + "mlp.e" + std::to_string(e) + ".";
+        put(pe + "gate", gu, e * 2 * Fn, Fn, W);
+        put(pe + "up", gu, e * 2 * Fn + Fn, Fn, W);
+        put(pe + "down", dn, e * W, W, Fn);
+      }
+      w.norm2 = n2; w.router = router; w.correction = corr; w.w_gu = gu; w.w_down = dn;
+    } else if (l.ff > 0 && l.ff_kind == HB_FF_GELU_TANH) {
+      const size_t Fn = l.ff;
+      uint8_t* n2 = take(W);
+      uint8_t* gu = take(2 * Fn * W);
+      uint8_t* dn = take(W * Fn);
+      put(p + "norm2", n2, 0, W, 1, true, gain_fill);
+      put(p + "mlp.gate", gu, 0, Fn, W);
+      put(p + "mlp.up", gu, Fn, Fn, W);
+      put(p + "mlp.down", dn, 0, W, Fn);
+      w.norm2 = n2; w.w_gu = gu; w.w_down = dn;
+    } else if (l.ff > 0) {
       const size_t Fn = l.ff;
       uint8_t* n2 = take(W);
       uint8_t* gu = take(2 * Fn * W);
       uint8_t* bgu = take(2 * Fn);
       uint8_t* dn = take(W * Fn);
       uint8_t* bdn = take(W);
-      put(p + "norm2", n2, 0, W, 1, true, 0.f);
+      put(p + "norm2", n2, 0, W, 1, true, gain_fill);
       put(p + "mlp.gate", gu, 0, Fn, W);
       put(p + "mlp.up", gu, Fn, Fn, W);
       put(p + "mlp.gate.b", bgu, 0, Fn, 1, false, 1.f, true);
@@ -318,7 +412,7 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
   }
   uint8_t* fn = take(W);
   uint8_t* head = take(V * W);
-  put("final.norm", fn, 0, W, 1, true, 0.f);
+  put("final.norm", fn, 0, W, 1, true, gain_fill);
   put("head", head, 0, V, W);
   if (m) {
     m->s_final_norm = fn;

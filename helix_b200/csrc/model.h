@@ -24,6 +24,7 @@ struct BertLayerW {
 // One layer of a layer-list decoder (HB_ARCH_RISEPEL).  Pointers are arena addresses of elements of Model::elem bytes.
 // Projections that read the same input are stacked into one weight (w_in) so one GEMM produces all of them:
 //   GLA:    rows [q | k | v | g | a1]            LATENT: rows [dq | dkv (own cache only) | g]
+//   GQA:    rows [q | k | v (unless the values are the keys) | g (one row per head, when gated)]
 struct StackLayerW {
   void *norm1 = nullptr, *norm2 = nullptr;
   void* w_in = nullptr;
@@ -35,7 +36,11 @@ struct StackLayerW {
   void* wo = nullptr;
   void *w_gu = nullptr, *b_gu = nullptr, *w_down = nullptr, *b_down = nullptr;  // feed-forward: rows [gate | up]
   size_t state_off = 0;  // GLA: float offset of this layer's [heads][dim][vdim] block inside a state slot
-  int cache_plane = -1;  // LATENT: plane of the latent pool this layer reads (its own, or the kv_from layer's)
+  int cache_plane = -1;  // LATENT: plane of the latent pool this layer reads (its own, or the kv_from layer's); GQA: its key plane
+  int cache_plane_v = -1;  // GQA: its value plane.  Both are [page][kv_head][page_size][dim | vdim]
+  // mixture of experts: router rows and choice corrections for experts + identity outputs; expert e's [gate | up] rows at
+  // w_gu + e * 2 ff * width, its down-projection at w_down + e * width * ff
+  void *router = nullptr, *correction = nullptr;
 };
 
 // where an uploaded checkpoint tensor lands inside the arena
@@ -64,9 +69,9 @@ struct Model {
   hb_stack_desc sd{};
   std::vector<hb_layer_desc> sl;
   std::vector<StackLayerW> sw;
-  void *s_embed = nullptr, *s_final_norm = nullptr, *s_head = nullptr;
+  void *s_embed = nullptr, *s_embed_norm = nullptr, *s_final_norm = nullptr, *s_head = nullptr;
   size_t state_floats = 0;              // fp32 state of one sequence over all GLA layers
-  std::vector<int> plane_row;           // latent pool planes: elements per cached row (kv_rank + rot_dim)
+  std::vector<int> plane_row;           // cache pool planes: elements per cached position (kv_rank + rot_dim; kv_heads * dim)
   int elem = 2;
   std::unordered_map<std::string, Placement> placements;  // HF checkpoint name -> arena slot
   std::unordered_map<std::string, bool> filled;
@@ -86,5 +91,8 @@ size_t arena_bytes_for(const hb_model_desc& d);
 void layout_model(Model& m);
 // Host inverse frequencies incl. llama3 scaling (HF transformers `_compute_llama3_parameters`).
 std::vector<float> rope_inv_freq(const hb_model_desc& d);
+// Rotation frequencies of a layer-list attention layer: base^(-2i/dims), i < dims/2, with the wavelength-dependent scaling
+// of hb_layer_desc (rope_factor <= 0: none), in double precision.
+std::vector<double> stack_rope_freqs(const hb_layer_desc& l);
 
 }  // namespace hb

@@ -1,0 +1,295 @@
+// Grouped-query attention of layer-list decoders over per-head key / value planes of the page pool
+// ([page][kv_head][page_size][D | Dv], bf16 or fp32): rotation + unit normalisation + cache write of a step's tokens, and the
+// attention of every token of a step — single decoded tokens and prompt portions alike — under a sliding-window, block
+// ("chunk") or causal mask, optionally with one extra unit in the softmax denominator and a sigmoid gate per head.
+// Softmax, normalisation and every sum are fp32; rotation angles are formed in double precision (position * frequency loses
+// bits that matter at positions in the thousands).  Summation orders are fixed per output element: a position's result does
+// not depend on what else the step carries.
+#include <math.h>
+
+#include <algorithm>
+
+#include "kernels.h"
+#include "launch.h"
+#include "stack_common.cuh"
+
+namespace hb {
+namespace {
+
+constexpr int kPrepThreads = 128;
+
+template <typename CT>
+__global__ void __launch_bounds__(kPrepThreads) gqa_prep_kernel(GqaPrepArgs a) {
+  extern __shared__ float sm[];
+  const int half = a.rope_dims / 2, Dp = (a.D + 3) / 4 * 4;
+  float* cs = sm;                                  // [half][2]: cos, sin of this token's angles
+  float* bufs = sm + ((2 * half + 3) / 4 * 4);     // one row buffer per warp
+  const int t = blockIdx.x, pos = a.positions[t];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    double s, c;
+    sincos((double)pos * a.freqs[i], &s, &c);
+    cs[2 * i] = (float)c;
+    cs[2 * i + 1] = (float)s;
+  }
+  __syncthreads();
+  const int slot = a.slots ? a.slots[t] : -1;
+  const size_t page = slot >= 0 ? slot / a.page_size : 0, off = slot >= 0 ? slot % a.page_size : 0;
+  const float* prow = a.p + (size_t)t * a.ldp;
+  float* buf = bufs + warp * Dp;
+  for (int u = warp; u < a.H + a.G; u += nw) {
+    const bool isq = u < a.H;
+    const int head = isq ? u : u - a.H;
+    const float* src = prow + (isq ? a.q_off : a.k_off) + (size_t)head * a.D;
+    for (int i = lane; i < a.D; i += 32) buf[i] = src[i];
+    __syncwarp();
+    for (int i = lane; i < half; i += 32) {
+      const int i0 = a.pairing ? 2 * i : i, i1 = a.pairing ? 2 * i + 1 : i + half;
+      const float x = buf[i0], y = buf[i1], c = cs[2 * i], s = cs[2 * i + 1];
+      buf[i0] = x * c - y * s;
+      buf[i1] = y * c + x * s;
+    }
+    __syncwarp();
+    float rs = 1.f;
+    if (a.unit_norm) {
+      float ss = 0.f;
+      for (int i = lane; i < a.D; i += 32) ss += buf[i] * buf[i];
+      ss = warp_sum(ss);
+      rs = 1.f / sqrtf(ss / (float)a.D + a.eps);
+    }
+    if (isq) {
+      float* dst = a.q + (size_t)t * a.ldq + (size_t)head * a.D;
+      bf16* dstb = a.q_b16 ? a.q_b16 + (size_t)t * a.ldq + (size_t)head * a.D : nullptr;
+      for (int i = lane; i < a.D; i += 32) {
+        const float v = buf[i] * rs;
+        dst[i] = v;
+        if (dstb) dstb[i] = __float2bfloat16(v);
+      }
+    } else if (slot >= 0) {
+      CT* row = (CT*)a.k_cache + ((page * a.G + head) * a.page_size + off) * a.D;
+      for (int i = lane; i < a.D; i += 32) stf<CT>(row, i, buf[i] * rs);
+    }
+    __syncwarp();
+  }
+  if (slot >= 0) {  // values leave the projection untouched
+    for (int e = threadIdx.x; e < a.G * a.Dv; e += blockDim.x) {
+      const int head = e / a.Dv, i = e % a.Dv;
+      CT* row = (CT*)a.v_cache + ((page * a.G + head) * a.page_size + off) * a.Dv;
+      stf<CT>(row, i, prow[a.v_off + (size_t)head * a.Dv + i]);
+    }
+  }
+}
+
+// One block per (token, kv head, group of up to kHG of its query heads): the heads of a group read the same key and value
+// rows, so one pass over them serves the group.
+//   scores:       one warp per key, lanes stride the row, HG dot products per loaded row
+//   softmax:      fp32, the optional unit of the denominator enters as a key of score 0 without a value
+//   weighted sum: thread (slice, column) adds the keys of its slice for all HG heads; slices are added in slice order
+// dynamic smem (floats): q [HG][Dp] | scores [max_keys][HG] | partials [threads][HG] | red [32 * HG] | row index [max_keys]
+constexpr int kAttThreads = 256;
+constexpr int kHG = 4;
+
+template <typename CT>
+__global__ void __launch_bounds__(kAttThreads) gqa_attn_kernel(GqaAttnArgs a, int max_keys) {
+  constexpr int HG = kHG;
+  extern __shared__ float sm[];
+  const int D = a.D, Dv = a.Dv, Dp = (D + 3) / 4 * 4;
+  float* qs = sm;
+  float* sc = qs + HG * Dp;
+  float* part = sc + (size_t)HG * max_keys;
+  float* red = part + HG * blockDim.x;
+  int* rowoff = reinterpret_cast<int*>(red + 32 * HG);
+  const int rep = a.H / a.G, parts = (rep + HG - 1) / HG;
+  const int t = blockIdx.x, g = blockIdx.y / parts, h0 = g * rep + (blockIdx.y % parts) * HG;
+  const int nh = min(HG, g * rep + rep - h0);
+  const int pos = a.positions[t];
+  int j0 = 0;
+  if (a.mask == MASK_CHUNK) j0 = pos / a.window * a.window;
+  else if (a.mask == MASK_WINDOW) j0 = max(0, pos - a.window + 1);
+  const int n = pos - j0 + 1;  // keys j0 .. pos (the host sized max_keys for the longest run any position can see)
+  const int32_t* pt = a.page_table + (size_t)a.seq_of[t] * a.max_pages;
+  for (int e = threadIdx.x; e < HG * Dp; e += blockDim.x) {
+    const int hh = e / Dp, i = e % Dp;
+    qs[e] = (hh < nh && i < D) ? a.q[(size_t)t * a.ldq + (size_t)(h0 + hh) * D + i] : 0.f;
+  }
+  for (int jj = threadIdx.x; jj < n; jj += blockDim.x) {
+    const int j = j0 + jj;
+    rowoff[jj] = (pt[j / a.page_size] * a.G + g) * a.page_size + j % a.page_size;
+  }
+  __syncthreads();
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const CT* kc = (const CT*)a.k_cache;
+  const CT* vc = (const CT*)a.v_cache;
+  if (sizeof(CT) == 2 && (D & 7) == 0) {
+    // bf16 rows that start on 16-byte boundaries: a lane takes 8 consecutive entries per load
+    for (int jj = w; jj < n; jj += nw) {
+      const bf16* row = reinterpret_cast<const bf16*>(kc) + (size_t)rowoff[jj] * D;
+      float s[HG] = {};
+      for (int i = l * 8; i < D; i += 256) {
+        const uint4 u = *reinterpret_cast<const uint4*>(row + i);
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(p2[e]);
+#pragma unroll
+          for (int hh = 0; hh < HG; ++hh) {
+            const float2 q = *reinterpret_cast<const float2*>(qs + hh * Dp + i + 2 * e);
+            s[hh] = fmaf(q.x, f.x, s[hh]);
+            s[hh] = fmaf(q.y, f.y, s[hh]);
+          }
+        }
+      }
+#pragma unroll
+      for (int hh = 0; hh < HG; ++hh) s[hh] = warp_sum(s[hh]);
+      if (l == 0) {
+#pragma unroll
+        for (int hh = 0; hh < HG; ++hh) sc[jj * HG + hh] = s[hh] * a.scale;
+      }
+    }
+  } else {
+    for (int jj = w; jj < n; jj += nw) {
+      const CT* row = kc + (size_t)rowoff[jj] * D;
+      float s[HG] = {};
+      for (int i = l; i < D; i += 32) {
+        const float kv = ldf<CT>(row, i);
+#pragma unroll
+        for (int hh = 0; hh < HG; ++hh) s[hh] = fmaf(qs[hh * Dp + i], kv, s[hh]);
+      }
+#pragma unroll
+      for (int hh = 0; hh < HG; ++hh) s[hh] = warp_sum(s[hh]);
+      if (l == 0) {
+#pragma unroll
+        for (int hh = 0; hh < HG; ++hh) sc[jj * HG + hh] = s[hh] * a.scale;
+      }
+    }
+  }
+  __syncthreads();
+  float mx[HG], inv[HG];
+#pragma unroll
+  for (int hh = 0; hh < HG; ++hh) mx[hh] = a.unit_sink ? 0.f : -INFINITY;
+  for (int jj = threadIdx.x; jj < n; jj += blockDim.x) {
+    const float4 v = *reinterpret_cast<const float4*>(sc + jj * HG);
+    mx[0] = fmaxf(mx[0], v.x); mx[1] = fmaxf(mx[1], v.y); mx[2] = fmaxf(mx[2], v.z); mx[3] = fmaxf(mx[3], v.w);
+  }
+#pragma unroll
+  for (int hh = 0; hh < HG; ++hh) mx[hh] = warp_max(mx[hh]);
+  if (l == 0) {
+#pragma unroll
+    for (int hh = 0; hh < HG; ++hh) red[w * HG + hh] = mx[hh];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int hh = 0; hh < HG; ++hh) mx[hh] = warp_max(l < nw ? red[l * HG + hh] : -INFINITY);
+  float sum[HG] = {};
+  for (int jj = threadIdx.x; jj < n; jj += blockDim.x) {
+    float4 v = *reinterpret_cast<const float4*>(sc + jj * HG);
+    v.x = expf(v.x - mx[0]); v.y = expf(v.y - mx[1]); v.z = expf(v.z - mx[2]); v.w = expf(v.w - mx[3]);
+    *reinterpret_cast<float4*>(sc + jj * HG) = v;
+    sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
+  }
+#pragma unroll
+  for (int hh = 0; hh < HG; ++hh) sum[hh] = warp_sum(sum[hh]);
+  __syncthreads();  // every thread has read the maxima
+  if (l == 0) {
+#pragma unroll
+    for (int hh = 0; hh < HG; ++hh) red[w * HG + hh] = sum[hh];
+  }
+  __syncthreads();  // also publishes the exponentials in sc[]
+#pragma unroll
+  for (int hh = 0; hh < HG; ++hh) {
+    const float tot = warp_sum(l < nw ? red[l * HG + hh] : 0.f) + (a.unit_sink ? expf(-mx[hh]) : 0.f);
+    float gate = 1.f;
+    if (a.gate && hh < nh) gate = sigmoidf_(a.gate[(size_t)t * a.ldg + h0 + hh]);
+    inv[hh] = gate / tot;
+  }
+  const int Rp = (Dv + 31) / 32 * 32;
+  const int NS = max(1, (int)blockDim.x / Rp);  // key slices
+  for (int r0 = 0; r0 < Dv; r0 += blockDim.x) {  // one pass unless a value row is wider than the block
+    const int sl = (NS > 1) ? threadIdx.x / Rp : 0, r = r0 + ((NS > 1) ? threadIdx.x % Rp : threadIdx.x);
+    float acc[HG] = {};
+    if (sl < NS && r < Dv) {
+      const CT* col = vc + r;
+      int jj = sl;
+      for (; jj + NS < n; jj += 2 * NS) {  // two independent loads in flight; the sum keeps key order
+        const float c0 = ldf<CT>(col, (size_t)rowoff[jj] * Dv), c1 = ldf<CT>(col, (size_t)rowoff[jj + NS] * Dv);
+        const float4 p0 = *reinterpret_cast<const float4*>(sc + jj * HG), p1 = *reinterpret_cast<const float4*>(sc + (jj + NS) * HG);
+        acc[0] = fmaf(p0.x, c0, acc[0]); acc[1] = fmaf(p0.y, c0, acc[1]); acc[2] = fmaf(p0.z, c0, acc[2]); acc[3] = fmaf(p0.w, c0, acc[3]);
+        acc[0] = fmaf(p1.x, c1, acc[0]); acc[1] = fmaf(p1.y, c1, acc[1]); acc[2] = fmaf(p1.z, c1, acc[2]); acc[3] = fmaf(p1.w, c1, acc[3]);
+      }
+      for (; jj < n; jj += NS) {
+        const float c0 = ldf<CT>(col, (size_t)rowoff[jj] * Dv);
+        const float4 p0 = *reinterpret_cast<const float4*>(sc + jj * HG);
+        acc[0] = fmaf(p0.x, c0, acc[0]); acc[1] = fmaf(p0.y, c0, acc[1]); acc[2] = fmaf(p0.z, c0, acc[2]); acc[3] = fmaf(p0.w, c0, acc[3]);
+      }
+    }
+    if (NS > 1) {
+      __syncthreads();
+#pragma unroll
+      for (int hh = 0; hh < HG; ++hh) part[threadIdx.x * HG + hh] = acc[hh];
+      __syncthreads();
+      if (threadIdx.x < Dv) {
+#pragma unroll
+        for (int hh = 0; hh < HG; ++hh) {
+          float tot = 0.f;
+          for (int ss = 0; ss < NS; ++ss) tot += part[(ss * Rp + threadIdx.x) * HG + hh];
+          if (hh < nh) {
+            const size_t o = (size_t)t * a.ldo + (size_t)(h0 + hh) * Dv + threadIdx.x;
+            const float v = tot * inv[hh];
+            a.out[o] = v;
+            if (a.out_b16) a.out_b16[o] = __float2bfloat16(v);
+          }
+        }
+      }
+    } else if (r < Dv) {
+#pragma unroll
+      for (int hh = 0; hh < HG; ++hh)
+        if (hh < nh) {
+          const size_t o = (size_t)t * a.ldo + (size_t)(h0 + hh) * Dv + r;
+          const float v = acc[hh] * inv[hh];
+          a.out[o] = v;
+          if (a.out_b16) a.out_b16[o] = __float2bfloat16(v);
+        }
+    }
+  }
+}
+
+}  // namespace
+
+size_t gqa_attn_smem(int D, int Dv, int max_keys) {
+  (void)Dv;
+  return ((size_t)kHG * ((D + 3) / 4 * 4) + (size_t)(kHG + 1) * max_keys + (size_t)kHG * kAttThreads + 32 * kHG) * 4;
+}
+
+cudaError_t stack_gqa_init() {
+  cudaError_t e;
+  const int big = 200 * 1024;
+  if ((e = cudaFuncSetAttribute(gqa_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(gqa_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big)) != cudaSuccess) return e;
+  return cudaSuccess;
+}
+
+cudaError_t gqa_prep(cudaStream_t s, const GqaPrepArgs& a) {
+  if (a.T <= 0) return cudaSuccess;
+  if (a.rope_dims % 2 || a.rope_dims > a.D || (a.rope_dims > 0 && !a.freqs)) return cudaErrorInvalidValue;
+  const size_t smem = ((size_t)(a.rope_dims + 3) / 4 * 4 + (size_t)(kPrepThreads / 32) * ((a.D + 3) / 4 * 4)) * 4;
+  if (a.f32) gqa_prep_kernel<float><<<a.T, kPrepThreads, smem, s>>>(a);
+  else gqa_prep_kernel<bf16><<<a.T, kPrepThreads, smem, s>>>(a);
+  return cudaGetLastError();
+}
+
+cudaError_t gqa_attn(cudaStream_t s, const GqaAttnArgs& a) {
+  if (a.T <= 0) return cudaSuccess;
+  if (a.G <= 0 || a.H % a.G || (a.mask != MASK_CAUSAL && a.window <= 0)) return cudaErrorInvalidValue;
+  // the longest run of keys any position of a sequence can see: window / block length, never more than a sequence holds
+  const int ctx = a.max_pages * a.page_size;
+  const int max_keys = a.mask == MASK_CAUSAL ? ctx : std::min(a.window, ctx);
+  const size_t smem = gqa_attn_smem(a.D, a.Dv, max_keys);
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;
+  const int rep = a.H / a.G;
+  dim3 grid(a.T, a.G * ((rep + kHG - 1) / kHG));
+  if (a.f32) gqa_attn_kernel<float><<<grid, kAttThreads, smem, s>>>(a, max_keys);
+  else gqa_attn_kernel<bf16><<<grid, kAttThreads, smem, s>>>(a, max_keys);
+  return cudaGetLastError();
+}
+
+}  // namespace hb

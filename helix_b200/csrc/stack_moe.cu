@@ -1,0 +1,200 @@
+// Feed-forward units of layer-list decoders beyond the clamped one: the plain gated unit (act(gate) * up with silu or
+// tanh-GELU) and the mixture of experts — router softmax and corrected top-k choice in fp32, expert units per (token,
+// choice), weighted combination with identity outputs.  Every sum has a fixed order per output element.
+#include <math.h>
+
+#include "kernels.h"
+#include "launch.h"
+#include "stack_common.cuh"
+
+namespace hb {
+namespace {
+
+__device__ __forceinline__ float gelu_tanh_(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float glu_act(float z, int act) { return act == GLU_GELU_TANH ? gelu_tanh_(z) : z * sigmoidf_(z); }
+
+// VEC = 4: F and ldg are multiples of four (16-byte loads and stores)
+template <int VEC>
+__global__ void gated_unit_kernel(const float* __restrict__ gu, long ldg, int act, float* __restrict__ out, bf16* __restrict__ outb, int F) {
+  const int t = blockIdx.x;
+  const int j = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+  if (j >= F) return;
+  if (VEC == 4) {
+    const float4 g = *reinterpret_cast<const float4*>(gu + (size_t)t * ldg + j);
+    const float4 u = *reinterpret_cast<const float4*>(gu + (size_t)t * ldg + F + j);
+    const float v0 = glu_act(g.x, act) * u.x, v1 = glu_act(g.y, act) * u.y, v2 = glu_act(g.z, act) * u.z, v3 = glu_act(g.w, act) * u.w;
+    *reinterpret_cast<float4*>(out + (size_t)t * F + j) = make_float4(v0, v1, v2, v3);
+    if (outb) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(v0, v1), hi = __floats2bfloat162_rn(v2, v3);
+      uint2 pk;
+      pk.x = *reinterpret_cast<unsigned*>(&lo);
+      pk.y = *reinterpret_cast<unsigned*>(&hi);
+      *reinterpret_cast<uint2*>(outb + (size_t)t * F + j) = pk;
+    }
+  } else {
+    const float v = glu_act(gu[(size_t)t * ldg + j], act) * gu[(size_t)t * ldg + F + j];
+    out[(size_t)t * F + j] = v;
+    if (outb) outb[(size_t)t * F + j] = __float2bfloat16(v);
+  }
+}
+
+// One warp per token.  dynamic smem: per warp R floats (the choice scores while the top-k is taken)
+template <typename WT>
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ z, long ldz, const WT* __restrict__ corr, int R,
+                                                        int top_k, int32_t* __restrict__ ids, float* __restrict__ wts, int T) {
+  extern __shared__ float sm[];
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + w;
+  if (t >= T) return;
+  float* pick = sm + (size_t)w * R;
+  const float* zr = z + (size_t)t * ldz;
+  float mx = -INFINITY;
+  for (int i = l; i < R; i += 32) mx = fmaxf(mx, zr[i]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int i = l; i < R; i += 32) sum += expf(zr[i] - mx);
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+  for (int i = l; i < R; i += 32) pick[i] = expf(zr[i] - mx) * inv + ldf<WT>(corr, i);
+  __syncwarp();
+  for (int k = 0; k < top_k; ++k) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = l; i < R; i += 32) {
+      const float v = pick[i];
+      if (v > best) { best = v; bi = i; }  // ascending i: the lowest index among equals stays
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (l == 0) {
+      ids[(size_t)t * top_k + k] = bi;
+      wts[(size_t)t * top_k + k] = expf(zr[bi] - mx) * inv;  // the score itself, without the correction
+      pick[bi] = -INFINITY;
+    }
+    __syncwarp();
+  }
+}
+
+// dot product of a weight row with a vector in shared memory, lanes striding the row; every lane gets the sum
+template <typename WT>
+__device__ __forceinline__ float warp_dot(const WT* __restrict__ wrow, const float* __restrict__ xs, int n, int lane) {
+  float s = 0.f;
+  if (sizeof(WT) == 2 && (n & 7) == 0 && ((uintptr_t)wrow & 15) == 0) {
+    for (int i = lane * 8; i < n; i += 256) {
+      const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(wrow) + i);
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(p2[e]);
+        s = fmaf(f.x, xs[i + 2 * e], s);
+        s = fmaf(f.y, xs[i + 2 * e + 1], s);
+      }
+    }
+  } else {
+    for (int i = lane; i < n; i += 32) s = fmaf(ldf<WT>(wrow, i), xs[i], s);
+  }
+  return warp_sum(s);
+}
+
+// block per (token, choice).  dynamic smem: x [Wp] + inner activation [F]
+template <typename WT>
+__global__ void __launch_bounds__(256) moe_expert_rows_kernel(const float* __restrict__ x, const bf16* __restrict__ xb,
+                                                              const WT* __restrict__ w_gu, const WT* __restrict__ w_down,
+                                                              const int32_t* __restrict__ ids, int E, int F, int W,
+                                                              float* __restrict__ y) {
+  extern __shared__ float sm[];
+  const int t = blockIdx.x;
+  const size_t item = (size_t)t * gridDim.y + blockIdx.y;  // (token, choice)
+  const int e = ids[item];
+  if (e >= E) return;
+  float* xs = sm;
+  float* hs = sm + (W + 3) / 4 * 4;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) xs[i] = xb ? __bfloat162float(xb[(size_t)t * W + i]) : x[(size_t)t * W + i];
+  __syncthreads();
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const WT* gu = w_gu + (size_t)e * 2 * F * W;
+  for (int f = w; f < F; f += nw) {
+    const float g = warp_dot<WT>(gu + (size_t)f * W, xs, W, l);
+    const float u = warp_dot<WT>(gu + (size_t)(F + f) * W, xs, W, l);
+    if (l == 0) {
+      float v = g * sigmoidf_(g) * u;
+      if (xb) v = __bfloat162float(__float2bfloat16(v));
+      hs[f] = v;
+    }
+  }
+  __syncthreads();
+  const WT* dn = w_down + (size_t)e * W * F;
+  for (int c = w; c < W; c += nw) {
+    const float v = warp_dot<WT>(dn + (size_t)c * F, hs, F, l);
+    if (l == 0) y[item * W + c] = v;
+  }
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ x, const float* __restrict__ y, const int32_t* __restrict__ ids,
+                                   const float* __restrict__ wts, int top_k, int E, float* __restrict__ out, int W) {
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top_k; ++k) {
+      const size_t item = (size_t)t * top_k + k;
+      const float v = ids[item] < E ? y[item * W + c] : x[(size_t)t * W + c];
+      acc = fmaf(wts[item], v, acc);
+    }
+    out[(size_t)t * W + c] = acc;
+  }
+}
+
+}  // namespace
+
+cudaError_t stack_moe_init() {
+  cudaError_t e;
+  const int big = 200 * 1024;
+  if ((e = cudaFuncSetAttribute(moe_expert_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(moe_expert_rows_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big)) != cudaSuccess) return e;
+  return cudaSuccess;
+}
+
+cudaError_t gated_unit(cudaStream_t s, const float* gu, long ldg, int act, float* out, bf16* outb, int T, int F) {
+  if (T <= 0) return cudaSuccess;
+  const bool vec = F % 4 == 0 && ldg % 4 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)outb & 7) == 0;
+  dim3 grid(T, ((vec ? F / 4 : F) + 255) / 256);
+  if (vec) gated_unit_kernel<4><<<grid, 256, 0, s>>>(gu, ldg, act, out, outb, F);
+  else gated_unit_kernel<1><<<grid, 256, 0, s>>>(gu, ldg, act, out, outb, F);
+  return cudaGetLastError();
+}
+
+cudaError_t moe_route(cudaStream_t s, const float* z, long ldz, const void* corr, bool f32, int R, int top_k, int32_t* ids, float* wts,
+                      int T) {
+  if (T <= 0) return cudaSuccess;
+  if (R <= 0 || top_k <= 0 || top_k > R || R > 1024) return cudaErrorInvalidValue;
+  const size_t smem = (size_t)4 * R * 4;
+  if (f32) moe_route_kernel<float><<<(T + 3) / 4, 128, smem, s>>>(z, ldz, (const float*)corr, R, top_k, ids, wts, T);
+  else moe_route_kernel<bf16><<<(T + 3) / 4, 128, smem, s>>>(z, ldz, (const bf16*)corr, R, top_k, ids, wts, T);
+  return cudaGetLastError();
+}
+
+cudaError_t moe_expert_rows(cudaStream_t s, const float* x, const bf16* xb, const void* w_gu, const void* w_down, bool f32,
+                            const int32_t* ids, int top_k, int E, int F, int W, float* y, int T) {
+  if (T <= 0) return cudaSuccess;
+  const size_t smem = ((size_t)(W + 3) / 4 * 4 + F) * 4;
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;
+  dim3 grid(T, top_k);
+  if (f32) moe_expert_rows_kernel<float><<<grid, 256, smem, s>>>(x, xb, (const float*)w_gu, (const float*)w_down, ids, E, F, W, y);
+  else moe_expert_rows_kernel<bf16><<<grid, 256, smem, s>>>(x, xb, (const bf16*)w_gu, (const bf16*)w_down, ids, E, F, W, y);
+  return cudaGetLastError();
+}
+
+cudaError_t moe_combine(cudaStream_t s, const float* x, const float* y, const int32_t* ids, const float* wts, int top_k, int E, float* out,
+                        int T, int W) {
+  if (T <= 0) return cudaSuccess;
+  moe_combine_kernel<<<T, 256, 0, s>>>(x, y, ids, wts, top_k, E, out, W);
+  return cudaGetLastError();
+}
+
+}  // namespace hb

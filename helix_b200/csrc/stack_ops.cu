@@ -7,38 +7,10 @@
 
 #include "kernels.h"
 #include "launch.h"
+#include "stack_common.cuh"
 
 namespace hb {
 namespace {
-
-template <typename T> __device__ __forceinline__ float ldf(const T* p, size_t i);
-template <> __device__ __forceinline__ float ldf<float>(const float* p, size_t i) { return p[i]; }
-template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p, size_t i) { return __bfloat162float(p[i]); }
-template <typename T> __device__ __forceinline__ void stf(T* p, size_t i, float v);
-template <> __device__ __forceinline__ void stf<float>(float* p, size_t i, float v) { p[i] = v; }
-template <> __device__ __forceinline__ void stf<bf16>(bf16* p, size_t i, float v) { p[i] = __float2bfloat16(v); }
-
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
-}
-// sum over the block; every thread gets the result.  red: >= 32 floats of shared memory.
-__device__ __forceinline__ float block_sum(float v, float* red) {
-  v = warp_sum(v);
-  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
-  __syncthreads();
-  if (l == 0) red[w] = v;
-  __syncthreads();
-  float t = (l < nw) ? red[l] : 0.f;
-  return warp_sum(t);
-}
-__device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-z)); }
 
 // ------------------------------------------------------------------ CUDA-core GEMM
 constexpr int GT = 64, GK = 16;
@@ -104,12 +76,14 @@ __global__ void embed_rows_kernel(const int32_t* __restrict__ tokens, const WT* 
   }
 }
 
-// out = rmsnorm(alpha * x + y + bias) * (off + w); y == nullptr: plain norm of x (alpha = 1).  dynamic smem: W floats + 32
+// out = rmsnorm(alpha * x + y + bias) * (off + w); y == nullptr: plain norm of x (alpha = 1).  add_x: the norm covers the
+// sublayer's output only and the stream is added afterwards, out = x + rmsnorm(y + bias) * (off + w).
+// dynamic smem: W floats + 32.  x / out are not __restrict__: the residual steps update the stream in place.
 template <typename WT>
-__global__ void __launch_bounds__(256) postnorm_kernel(const float* __restrict__ x, const int32_t* __restrict__ row_index,
+__global__ void __launch_bounds__(256) postnorm_kernel(const float* x, const int32_t* __restrict__ row_index,
                                                        const float* __restrict__ y, long ldy, const WT* __restrict__ bias,
                                                        const WT* __restrict__ w, float alpha, float off, float eps,
-                                                       float* __restrict__ out, bf16* __restrict__ outb, int W) {
+                                                       float* out, bf16* __restrict__ outb, int W, int add_x) {
   extern __shared__ float sm[];
   float* row = sm;
   float* red = sm + W;
@@ -117,7 +91,7 @@ __global__ void __launch_bounds__(256) postnorm_kernel(const float* __restrict__
   const size_t src = row_index ? (size_t)row_index[r] : (size_t)r;
   float ss = 0.f;
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    float v = x[src * W + i];
+    float v = add_x ? 0.f : x[src * W + i];
     if (y) v = alpha * v + y[(size_t)r * ldy + i] + (bias ? ldf<WT>(bias, i) : 0.f);
     row[i] = v;
     ss += v * v;
@@ -125,7 +99,8 @@ __global__ void __launch_bounds__(256) postnorm_kernel(const float* __restrict__
   ss = block_sum(ss, red);
   const float rs = 1.f / sqrtf(ss / (float)W + eps);
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float v = row[i] * rs * (off + ldf<WT>(w, i));
+    float v = row[i] * rs * (off + ldf<WT>(w, i));
+    if (add_x) v += x[src * W + i];
     out[(size_t)r * W + i] = v;
     if (outb) outb[(size_t)r * W + i] = __float2bfloat16(v);
   }
@@ -134,10 +109,10 @@ __global__ void __launch_bounds__(256) postnorm_kernel(const float* __restrict__
 // The same step with the row held in registers as float4 (W a multiple of 4, W <= 4 * 256 * kPnChunks)
 constexpr int kPnChunks = 8;
 template <typename WT>
-__global__ void __launch_bounds__(256) postnorm_vec_kernel(const float* __restrict__ x, const int32_t* __restrict__ row_index,
+__global__ void __launch_bounds__(256) postnorm_vec_kernel(const float* x, const int32_t* __restrict__ row_index,
                                                            const float* __restrict__ y, long ldy, const WT* __restrict__ bias,
                                                            const WT* __restrict__ w, float alpha, float off, float eps,
-                                                           float* __restrict__ out, bf16* __restrict__ outb, int W) {
+                                                           float* out, bf16* __restrict__ outb, int W, int add_x) {
   __shared__ float red[32];
   const int r = blockIdx.x;
   const size_t src = row_index ? (size_t)row_index[r] : (size_t)r;
@@ -148,7 +123,7 @@ __global__ void __launch_bounds__(256) postnorm_vec_kernel(const float* __restri
   for (int c = 0; c < kPnChunks; ++c) {
     const int i = threadIdx.x + c * 256;
     if (i < nv) {
-      float4 a = *reinterpret_cast<const float4*>(x + src * W + 4 * i);
+      float4 a = add_x ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(x + src * W + 4 * i);
       if (y) {
         const float4 b = *reinterpret_cast<const float4*>(y + (size_t)r * ldy + 4 * i);
         a.x = alpha * a.x + b.x + (bias ? ldf<WT>(bias, 4 * i) : 0.f);
@@ -171,6 +146,10 @@ __global__ void __launch_bounds__(256) postnorm_vec_kernel(const float* __restri
       a.y *= rs * (off + ldf<WT>(w, 4 * i + 1));
       a.z *= rs * (off + ldf<WT>(w, 4 * i + 2));
       a.w *= rs * (off + ldf<WT>(w, 4 * i + 3));
+      if (add_x) {
+        const float4 b = *reinterpret_cast<const float4*>(x + src * W + 4 * i);
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+      }
       *reinterpret_cast<float4*>(out + (size_t)r * W + 4 * i) = a;
       if (outb) {
         __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
@@ -770,28 +749,34 @@ cudaError_t embed_rows_f32(cudaStream_t s, const int32_t* tokens, const void* ta
 }
 
 static cudaError_t postnorm_launch(cudaStream_t s, const float* x, const int32_t* idx, const float* y, long ldy, const void* bias,
-                                   const void* w, bool f32, float alpha, float off, float eps, float* out, bf16* outb, int rows, int W) {
+                                   const void* w, bool f32, float alpha, float off, float eps, float* out, bf16* outb, int rows, int W,
+                                   int add_x = 0) {
   if (rows <= 0) return cudaSuccess;
   if (W % 4 == 0 && W <= 4 * 256 * kPnChunks && (!y || ldy % 4 == 0) && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0 &&
       ((uintptr_t)out & 15) == 0 && ((uintptr_t)outb & 7) == 0) {
     if (f32)
-      postnorm_vec_kernel<float><<<rows, 256, 0, s>>>(x, idx, y, ldy, (const float*)bias, (const float*)w, alpha, off, eps, out, outb, W);
+      postnorm_vec_kernel<float><<<rows, 256, 0, s>>>(x, idx, y, ldy, (const float*)bias, (const float*)w, alpha, off, eps, out, outb, W, add_x);
     else
-      postnorm_vec_kernel<bf16><<<rows, 256, 0, s>>>(x, idx, y, ldy, (const bf16*)bias, (const bf16*)w, alpha, off, eps, out, outb, W);
+      postnorm_vec_kernel<bf16><<<rows, 256, 0, s>>>(x, idx, y, ldy, (const bf16*)bias, (const bf16*)w, alpha, off, eps, out, outb, W, add_x);
     return KERR();
   }
   const size_t smem = (size_t)(W + 32) * 4;
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
   if (f32)
-    postnorm_kernel<float><<<rows, 256, smem, s>>>(x, idx, y, ldy, (const float*)bias, (const float*)w, alpha, off, eps, out, outb, W);
+    postnorm_kernel<float><<<rows, 256, smem, s>>>(x, idx, y, ldy, (const float*)bias, (const float*)w, alpha, off, eps, out, outb, W, add_x);
   else
-    postnorm_kernel<bf16><<<rows, 256, smem, s>>>(x, idx, y, ldy, (const bf16*)bias, (const bf16*)w, alpha, off, eps, out, outb, W);
+    postnorm_kernel<bf16><<<rows, 256, smem, s>>>(x, idx, y, ldy, (const bf16*)bias, (const bf16*)w, alpha, off, eps, out, outb, W, add_x);
   return KERR();
 }
 cudaError_t resid_postnorm(cudaStream_t s, float* x, bf16* xb, const float* y, long ldy, const void* bias, const void* w, bool f32,
                            float alpha, float off, float eps, int T, int W) {
   if (!y) return cudaErrorInvalidValue;
   return postnorm_launch(s, x, nullptr, y, ldy, bias, w, f32, alpha, off, eps, x, xb, T, W);
+}
+cudaError_t resid_add_normed(cudaStream_t s, float* x, bf16* xb, const float* y, long ldy, const void* bias, const void* w, bool f32,
+                             float off, float eps, int T, int W) {
+  if (!y) return cudaErrorInvalidValue;
+  return postnorm_launch(s, x, nullptr, y, ldy, bias, w, f32, 1.f, off, eps, x, xb, T, W, 1);
 }
 cudaError_t norm_rows_f32(cudaStream_t s, const float* x, const int32_t* row_index, const void* w, bool f32, float off, float eps,
                           float* out, bf16* outb, int rows, int W) {

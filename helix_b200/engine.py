@@ -77,6 +77,11 @@ class ModelDesc:
 
 MIXER_GLA = 0
 MIXER_LATENT = 1
+MIXER_GQA = 2
+MASK_WINDOW, MASK_CHUNK, MASK_CAUSAL = 0, 1, 2
+FF_CLAMPED, FF_GELU_TANH, FF_MOE = 0, 1, 2
+NORM_OF_SUM, NORM_OF_OUTPUT = 0, 1
+ATTN_QK_UNIT_NORM, ATTN_V_IS_K, ATTN_UNIT_SINK, ATTN_HEAD_GATE = 1, 2, 4, 8
 
 
 @dataclass
@@ -98,10 +103,24 @@ class LayerDesc:
     scale: float = 1.0
     ff: int = 0
     ff_limit: float = 0.0
+    kv_heads: int = 0          # GQA
+    mask: int = MASK_WINDOW
+    attn_flags: int = 0
+    rope_pairing: int = 0      # 1: interleaved pairs (2i, 2i+1)
+    rope_factor: float = 0.0   # <= 0: no frequency scaling
+    rope_low: float = 1.0
+    rope_high: float = 4.0
+    rope_original: int = 0
+    ff_kind: int = FF_CLAMPED
+    experts: int = 0           # FF_MOE: experts with weights (ff = inner size of one)
+    identity_experts: int = 0
+    top_k: int = 0
 
     def to_c(self):
         return LayerDescC(self.mixer, self.heads, self.dim, self.vdim, self.tau, self.decay_rank, self.q_rank, self.kv_rank,
-                          self.rot_dim, self.rope_dims, self.window, self.kv_from, self.rope_base, self.scale, self.ff, self.ff_limit)
+                          self.rot_dim, self.rope_dims, self.window, self.kv_from, self.rope_base, self.scale, self.ff, self.ff_limit,
+                          self.kv_heads, self.mask, self.attn_flags, self.rope_pairing, self.rope_factor, self.rope_low,
+                          self.rope_high, self.rope_original, self.ff_kind, self.experts, self.identity_experts, self.top_k)
 
 
 @dataclass
@@ -114,6 +133,9 @@ class StackDesc:
     norm_eps: float = 1e-6
     resid_alpha: float = 1.0
     logit_softcap: float = 0.0
+    norm_place: int = NORM_OF_SUM
+    embed_norm: int = 0
+    plain_gains: int = 0
     arch: int = 2
 
     @property
@@ -127,7 +149,7 @@ class StackDesc:
     def to_c(self):
         arr = (LayerDescC * len(self.layers))(*[l.to_c() for l in self.layers])
         return StackDescC(self.width, self.vocab, len(self.layers), self.compute_f32, self.norm_eps, self.resid_alpha,
-                          self.logit_softcap), arr
+                          self.logit_softcap, self.norm_place, self.embed_norm, self.plain_gains), arr
 
 
 @dataclass

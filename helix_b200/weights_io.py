@@ -11,7 +11,8 @@ import struct
 
 import numpy as np
 
-from .engine import LayerDesc, ModelDesc, StackDesc, bf16_bits, MIXER_GLA, MIXER_LATENT
+from . import engine as _e
+from .engine import LayerDesc, ModelDesc, StackDesc, bf16_bits, MIXER_GLA, MIXER_LATENT, MIXER_GQA
 
 _DT = {"BF16": (np.uint16, 2), "F16": (np.float16, 2), "F32": (np.float32, 4)}
 _IGNORED = ("pooler.", "embeddings.position_ids", "rotary_emb.inv_freq", "cls.", "visual.")  # visual.: the VL tower (not served)
@@ -122,14 +123,58 @@ def risepel_desc(cfg, shapes=None, compute_f32=False):
                      logit_softcap=float(cfg.get("logit_softcap") or 0.0))
 
 
+def lurepel_desc(cfg, shapes=None, compute_f32=False):
+    """config.json of a Lurepel checkpoint -> StackDesc: grouped-query attention layers whose values are their keys, on a
+    stream where each sublayer's output is normed before it is added; dense (tanh-GELU) or mixture-of-experts feed-forward.
+    Every size and constant comes from the configuration."""
+    layers = []
+    for i, ly in enumerate(cfg["layers"]):
+        if ly["type"] != "attention":
+            raise ValueError(f"layer {i}: unknown layer type {ly['type']!r}")
+        m = ly["mixer"]
+        d = LayerDesc(mixer=MIXER_GQA, heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                      scale=float(m["scale"]),
+                      attn_flags=_e.ATTN_QK_UNIT_NORM | _e.ATTN_V_IS_K | _e.ATTN_UNIT_SINK | _e.ATTN_HEAD_GATE)
+        mask = m.get("mask")
+        if mask and mask.get("size"):
+            d.mask, d.window = _e.MASK_CHUNK, int(mask["size"])
+        else:
+            d.mask, d.window = _e.MASK_CAUSAL, 0
+        rot = m.get("rot")
+        if rot and rot.get("dims"):
+            d.rope_dims, d.rope_base, d.rope_pairing = int(rot["dims"]), float(rot["base"]), 1
+            sc = rot.get("scaling")
+            if sc:
+                d.rope_factor, d.rope_low, d.rope_high = float(sc["factor"]), float(sc["low"]), float(sc["high"])
+                d.rope_original = int(sc["original"])
+        mlp = ly.get("mlp")
+        if mlp is not None:
+            kind = mlp.get("kind")
+            if kind == "dense":
+                d.ff_kind, d.ff = _e.FF_GELU_TANH, int(mlp["ff"])
+            elif kind == "moe":
+                r = mlp["router"]
+                d.ff_kind, d.ff = _e.FF_MOE, int(mlp["expert"]["ff"])
+                d.experts, d.identity_experts, d.top_k = int(r["experts"]), int(r.get("identity") or 0), int(r["top"])
+            else:
+                raise ValueError(f"layer {i}: unsupported feed-forward kind {kind!r}")
+        layers.append(d)
+    return StackDesc(width=int(cfg["width"]), vocab=int(cfg["vocab"]), layers=layers, compute_f32=int(bool(compute_f32)),
+                     norm_eps=float(cfg["norm"]["eps"]), resid_alpha=1.0, logit_softcap=0.0, norm_place=_e.NORM_OF_OUTPUT,
+                     embed_norm=1, plain_gains=1)
+
+
+STACK_READERS = {"Risepel": risepel_desc, "Lurepel": lurepel_desc}  # layer-list decoders by config.json "architecture"
+
+
 def desc_from_hf_config(cfg, shapes=None, compute_f32=False):
     """config.json (dict or path) -> ModelDesc (Llama- and Qwen2-family decoders, BERT-family encoders) or StackDesc
-    (layer-list decoders: "architecture": "Risepel"; `shapes` = safetensors_shapes of the checkpoint)."""
+    (layer-list decoders: "architecture" names one of STACK_READERS; `shapes` = safetensors_shapes of the checkpoint)."""
     if not isinstance(cfg, dict):
         with open(cfg) as f:
             cfg = json.load(f)
-    if cfg.get("architecture") == "Risepel":
-        return risepel_desc(cfg, shapes, compute_f32)
+    if cfg.get("architecture") in STACK_READERS:
+        return STACK_READERS[cfg["architecture"]](cfg, shapes, compute_f32)
     if compute_f32:
         raise ValueError("fp32 compute exists for layer-list decoders only")
     mt = cfg.get("model_type", "")

@@ -46,7 +46,7 @@
 extern "C" {
 #endif
 
-#define HB_ABI_VERSION 3
+#define HB_ABI_VERSION 4
 
 typedef enum hb_status {
   HB_OK = 0,
@@ -61,8 +61,10 @@ typedef enum hb_status {
 typedef enum hb_arch {
   HB_ARCH_LLAMA = 0,
   HB_ARCH_BERT = 1,
-  HB_ARCH_RISEPEL = 2 /* layer-list decoders (hb_stack_desc + hb_layer_desc[]): recurrent and windowed-attention mixers on a
-                         32-bit post-norm residual stream; loaded with hb_model_load_begin_stack */
+  HB_ARCH_RISEPEL = 2, /* layer-list decoders (hb_stack_desc + hb_layer_desc[]): recurrent, latent-attention and grouped-query
+                          mixers, gated / clamped / mixture-of-experts feed-forwards on a 32-bit residual stream (the Risepel
+                          and Lurepel designs are two settings of it); loaded with hb_model_load_begin_stack */
+  HB_ARCH_STACK = 2
 } hb_arch;
 
 typedef struct hb_engine hb_engine;
@@ -124,30 +126,64 @@ typedef struct hb_model_desc {
  *                         expanded from a shared latent (kv_rank) plus one rotary key part (rot_dim) shared by all heads;
  *                         sliding window, learned per-head sink in the softmax denominator, sigmoid output gate.  kv_from >= 0:
  *                         the layer has no down-projection of its own and reads the cache rows of that earlier layer.
- *      A layer is x <- norm(alpha x + mixer(x)) and, when ff > 0, x <- norm(alpha x + ff(x)) with the clamped gated unit
- *      g = min(gate, limit), u = clamp(up, +-limit), y = g sigmoid(1.702 g) (u + 1).  Norm gains are stored as offsets from 1.
- *      Logits are soft-capped: cap * tanh(z / cap) (cap <= 0: off).  Tensor names: embed, final.norm, head, l<i>.norm1/2,
- *      l<i>.mix.{q,k,v,g,o,norm,a1,a2,a2.b | dq,dq.norm,uq,dkv,dkv.norm,uk,uv,sink,g,o}, l<i>.mlp.{gate,up,down}[.b]. ---- */
-typedef enum hb_mixer { HB_MIXER_GLA = 0, HB_MIXER_LATENT = 1 } hb_mixer;
+ *        HB_MIXER_GQA     grouped-query attention over cached per-head keys and values (kv_heads of them; query head h reads
+ *                         head h / (heads / kv_heads)).  rope_dims leading entries of q and k rotate (rope_pairing, optional
+ *                         wavelength-dependent frequency scaling rope_factor / rope_low / rope_high / rope_original); the
+ *                         attn_flags choose: unit-RMS normalisation of rotated q and k, values = the key projection as it
+ *                         leaves the matrix product (no value matrix), one unit added to the softmax denominator, a sigmoid
+ *                         gate per head from its own projection row.  mask: sliding window, or blocks of `window` positions
+ *                         counted from position 0 of the sequence, or plain causal.
+ *      Residual step (hb_stack_desc.norm_place): HB_NORM_OF_SUM x <- norm(alpha x + f(x)), or HB_NORM_OF_OUTPUT
+ *      x <- x + norm(f(x)); f = mixer and, when ff > 0, the feed-forward (ff_kind):
+ *        HB_FF_CLAMPED    g = min(gate, limit), u = clamp(up, +-limit), y = down(g sigmoid(1.702 g) (u + 1)), with biases
+ *        HB_FF_GELU_TANH  y = down(gelu_tanh(gate) * up), no biases
+ *        HB_FF_MOE        experts small units down(silu(gate) * up) of inner size ff plus identity_experts outputs that return
+ *                         their input; router scores = softmax over all experts + identity outputs in fp32; the top_k largest
+ *                         of (score + correction) are chosen and weighted by their scores (not renormalised).
+ *      Norm gains are stored as offsets from 1 unless plain_gains.  embed_norm: the embedding row is normed (embed.norm) before
+ *      the first layer.  Logits are soft-capped: cap * tanh(z / cap) (cap <= 0: off).  Tensor names: embed[.norm], final.norm,
+ *      head, l<i>.norm1/2, l<i>.mix.{q,k,v,g,o,norm,a1,a2,a2.b | dq,dq.norm,uq,dkv,dkv.norm,uk,uv,sink,g,o | q,k,[v,]g,o},
+ *      l<i>.mlp.{gate,up,down}[.b] or l<i>.mlp.{router,correction,e<j>.gate,e<j>.up,e<j>.down}. ---- */
+typedef enum hb_mixer { HB_MIXER_GLA = 0, HB_MIXER_LATENT = 1, HB_MIXER_GQA = 2 } hb_mixer;
+typedef enum hb_mask { HB_MASK_WINDOW = 0, HB_MASK_CHUNK = 1, HB_MASK_CAUSAL = 2 } hb_mask;
+typedef enum hb_ff_kind { HB_FF_CLAMPED = 0, HB_FF_GELU_TANH = 1, HB_FF_MOE = 2 } hb_ff_kind;
+typedef enum hb_norm_place { HB_NORM_OF_SUM = 0, HB_NORM_OF_OUTPUT = 1 } hb_norm_place;
+enum {
+  HB_ATTN_QK_UNIT_NORM = 1,  /* q and k divided by their root mean square over dim after rotation (no gain) */
+  HB_ATTN_V_IS_K = 2,        /* values are the key projections before rotation and normalisation; no mix.v tensor */
+  HB_ATTN_UNIT_SINK = 4,     /* p_j = exp(s_j) / (1 + sum exp(s_i)) */
+  HB_ATTN_HEAD_GATE = 8      /* head h's output times sigmoid(row h of mix.g applied to the layer input) */
+};
 typedef struct hb_layer_desc {
   int32_t mixer;       /* hb_mixer */
   int32_t heads, dim, vdim;
   float tau;           /* GLA: decay temperature */
   int32_t decay_rank;  /* GLA: inner size of the decay projection (rows of a1) */
   int32_t q_rank, kv_rank, rot_dim; /* LATENT */
-  int32_t rope_dims;   /* leading entries of the rot_dim part that rotate (rotate-half pairing i <-> i + rope_dims/2) */
-  int32_t window;      /* position i sees j with 0 <= i - j < window */
+  int32_t rope_dims;   /* LATENT: leading entries of the rot_dim part that rotate; GQA: leading entries of each head */
+  int32_t window;      /* HB_MASK_WINDOW: position i sees j with 0 <= i - j < window; HB_MASK_CHUNK: block length */
   int32_t kv_from;     /* < 0: own cache rows */
   float rope_base, scale;
-  int32_t ff;          /* 0: the layer has no feed-forward sublayer */
+  int32_t ff;          /* 0: the layer has no feed-forward sublayer; HB_FF_MOE: inner size of one expert */
   float ff_limit;
+  int32_t kv_heads;    /* GQA */
+  int32_t mask;        /* hb_mask (GQA; LATENT layers are HB_MASK_WINDOW) */
+  int32_t attn_flags;  /* HB_ATTN_* (GQA) */
+  int32_t rope_pairing;  /* 0: entry i pairs with i + rope_dims/2; 1: entry 2i pairs with 2i+1 (GQA) */
+  float rope_factor, rope_low, rope_high; /* GQA: frequency scaling, rope_factor <= 0: off.  With wavelength l = 2 pi / f: f stays */
+  int32_t rope_original;                  /* where l < original/high, becomes f/factor where l > original/low, blends between */
+  int32_t ff_kind;     /* hb_ff_kind */
+  int32_t experts, identity_experts, top_k; /* HB_FF_MOE: experts with weights, outputs that return their input, chosen per token */
   int32_t reserved[4];
 } hb_layer_desc;
 typedef struct hb_stack_desc {
   int32_t width, vocab, n_layers;
   int32_t compute_f32; /* 1: weights, cache rows and every product in true fp32 (CUDA-core FMA; the exact mode) */
   float norm_eps, resid_alpha, logit_softcap;
-  int32_t reserved[5];
+  int32_t norm_place;  /* hb_norm_place */
+  int32_t embed_norm;  /* 1: x = norm(embed[token]) with gain embed.norm */
+  int32_t plain_gains; /* 1: norm gains apply as stored; 0: stored as offsets from one */
+  int32_t reserved[2];
 } hb_stack_desc;
 
 typedef struct hb_sampling {
