@@ -110,6 +110,7 @@ def attention_mixer(h, p, m, eps, pos=None, past=None):
     else:
         kpos = pos
     size = (m.get("mask") or {}).get("size")
+    unit = 1.0 if m.get("sink", True) else 0.0  # the design always has it; tests switch it off to show that it matters
     gate = sigmoid(h @ p["g"].T)  # [T, H]
     out = np.zeros((T, H, v.shape[-1]), F)
     for t in range(T):
@@ -117,9 +118,9 @@ def attention_mixer(h, p, m, eps, pos=None, past=None):
         for hh in range(H):
             g = hh // (H // G)
             s = (kn[see, g] @ q[t, hh]) * m["scale"]
-            mx = max(0.0, s.max()) if s.size else 0.0
+            mx = max(0.0, s.max())
             e = np.exp(s - mx)
-            pr = e / (np.exp(-mx) + e.sum())  # one unit of weight (score 0) belongs to nothing
+            pr = e / (unit * np.exp(-mx) + e.sum())  # one unit of weight (score 0) belongs to nothing
             out[t, hh] = pr @ v[see, g]
     out = out * gate[:, :, None]
     return out.reshape(T, -1) @ p["o"].T, (kn, v, kpos)
@@ -140,6 +141,14 @@ def moe_route(h, p, r):
     pick = s + np.asarray(p["correction"], F)
     idx = np.argsort(-pick, axis=-1, kind="stable")[:, :r["top"]]
     return idx, np.take_along_axis(s, idx, -1)
+
+
+def route_margin(h, p, r):
+    """Per token: how far the last chosen output's choice score lies above the best one left out (inf when all are chosen)."""
+    z = np.asarray(h, F) @ p["router"].T
+    s = np.exp(z - z.max(-1, keepdims=True))
+    pick = -np.sort(-(s / s.sum(-1, keepdims=True) + np.asarray(p["correction"], F)), axis=-1)
+    return pick[:, r["top"] - 1] - pick[:, r["top"]] if pick.shape[1] > r["top"] else np.full(len(pick), np.inf)
 
 
 def moe_ff(h, p, r):
@@ -199,3 +208,114 @@ def forward(cfg, sd, tokens, trace=None):
         if trace is not None:
             trace.append(x.copy())
     return norm_gain(x, P["final_norm"], eps) @ P["head"].T
+
+
+class LurepelOracle:
+    """The decoder over a checkpoint, fed in portions: `state` keeps every layer's keys and values of the tokens seen."""
+
+    def __init__(self, cfg, sd):
+        self.cfg = cfg
+        self.P = split_params(sd, len(cfg["layers"]))
+        self.eps = float(cfg["norm"]["eps"])
+
+    def new_state(self):
+        return dict(pos=0, kv={})
+
+    def forward(self, tokens, state=None, taps=None, margins=None):
+        """The next tokens of one sequence -> logits [T, vocab].  taps / margins (lists) receive the stream after every
+        layer / every router's choice margins per token."""
+        P, eps = self.P, self.eps
+        st = state if state is not None else self.new_state()
+        T = len(tokens)
+        pos = st["pos"] + np.arange(T)
+        x = norm_gain(P["embed"][np.asarray(tokens)], P["embed_norm"], eps)
+        for i, (ly, p) in enumerate(zip(self.cfg["layers"], P["layers"])):
+            if ly["type"] != "attention":
+                raise ValueError(ly["type"])
+            y, st["kv"][i] = attention_mixer(x, p["mix"], ly["mixer"], eps, pos, st["kv"].get(i))
+            x = x + norm_gain(y, p["norm1"], eps)
+            mlp = ly.get("mlp")
+            if mlp:
+                if margins is not None and mlp["kind"] == "moe":
+                    margins.append(route_margin(x, p["mlp"], mlp["router"]))
+                y = dense_ff(x, p["mlp"]) if mlp["kind"] == "dense" else moe_ff(x, p["mlp"], mlp["router"])
+                x = x + norm_gain(y, p["norm2"], eps)
+            if taps is not None:
+                taps.append(x.copy())
+        st["pos"] += T
+        return norm_gain(x, P["final_norm"], eps) @ P["head"].T
+
+    def greedy(self, prompt, n):
+        st = self.new_state()
+        z = self.forward(prompt, st)[-1]
+        out, rows = [], []
+        for _ in range(n):
+            rows.append(z)
+            out.append(int(np.argmax(z)))
+            z = self.forward([out[-1]], st)[-1]
+        return out, np.stack(rows)
+
+
+# ------------------------------------------------------------------ random checkpoints for tests
+def random_config(width=80, vocab=150, order=("dense", "moe", None), heads=6, kv_heads=2, dim=24, chunk=20, rot_dims=16,
+                  base=5000.0, scaling=dict(factor=4.0, low=1.0, high=3.0, original=64), scale=None, ff=72, expert_ff=40,
+                  experts=5, identity=2, top=3, eps=1e-5, per_layer=None):
+    """A small configuration; `order` lists each layer's feed-forward ("dense", "moe" or None), per_layer[i] overrides
+    mixer keys of layer i.  The default scaling band (wavelengths 64/3 .. 64) has rotary pairs below, inside and above it."""
+    layers = []
+    for i, kind in enumerate(order):
+        mixer = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=float(scale if scale is not None else 3.0 / math.sqrt(dim)))
+        if chunk:
+            mixer["mask"] = dict(size=chunk)
+        if rot_dims:
+            mixer["rot"] = dict(base=base, dims=rot_dims)
+            if scaling:
+                mixer["rot"]["scaling"] = dict(scaling)
+        mixer.update((per_layer or {}).get(i, {}))
+        mixer["vdim"] = mixer["dim"]
+        if kind == "dense":
+            mlp = dict(kind="dense", ff=ff)
+        elif kind == "moe":
+            mlp = dict(kind="moe", expert=dict(ff=expert_ff), router=dict(experts=experts, identity=identity, top=top))
+        else:
+            mlp = None
+        layers.append(dict(type="attention", mixer=mixer, mlp=mlp))
+    return dict(architecture="Lurepel", width=width, vocab=vocab, layers=layers, norm=dict(eps=eps))
+
+
+def random_state_dict(cfg, seed=0):
+    from .weights import _t
+    W, V = cfg["width"], cfg["vocab"]
+    s = lambda n: 1.0 / math.sqrt(n)
+    sd = {"embed": _t(seed, "embed", (V, W), 1.0), "embed.norm": _t(seed, "en", (W,), 0.1, 1.0),
+          "final.norm": _t(seed, "fn", (W,), 0.1, 1.0), "head": _t(seed, "head", (V, W), s(W))}
+    for i, ly in enumerate(cfg["layers"]):
+        m, p = ly["mixer"], f"l{i}."
+        H, G, D = m["heads"], m["kv_heads"], m["dim"]
+        sd[p + "norm1"] = _t(seed, p + "n1", (W,), 0.1, 1.0)
+        sd[p + "mix.q"] = _t(seed, p + "q", (H * D, W), s(W))
+        sd[p + "mix.k"] = _t(seed, p + "k", (G * D, W), s(W))
+        sd[p + "mix.g"] = _t(seed, p + "g", (H, W), 2.0 * s(W))
+        sd[p + "mix.o"] = _t(seed, p + "o", (W, H * D), s(H * D))
+        mlp = ly.get("mlp")
+        if not mlp:
+            continue
+        sd[p + "norm2"] = _t(seed, p + "n2", (W,), 0.1, 1.0)
+        if mlp["kind"] == "dense":
+            Fn = mlp["ff"]
+            sd[p + "mlp.gate"] = _t(seed, p + "gate", (Fn, W), 2.0 * s(W))
+            sd[p + "mlp.up"] = _t(seed, p + "up", (Fn, W), 2.0 * s(W))
+            sd[p + "mlp.down"] = _t(seed, p + "down", (W, Fn), s(Fn))
+        else:
+            r, Fn = mlp["router"], mlp["expert"]["ff"]
+            R = r["experts"] + r.get("identity", 0)
+            sd[p + "mlp.router"] = _t(seed, p + "router", (R, W), 3.0 * s(W))
+            # choice corrections on a grid of 0.08, shuffled: no two outputs tie by their corrections alone, so a choice is
+            # a close call only where two scores happen to differ by a grid step
+            from .weights import _rng, to_bf16_f32
+            sd[p + "mlp.correction"] = to_bf16_f32((_rng(seed, p + "corr").permutation(R) - (R - 1) / 2.0) * 0.08)
+            for e in range(r["experts"]):
+                sd[p + f"mlp.e{e}.gate"] = _t(seed, p + f"e{e}g", (Fn, W), 2.0 * s(W))
+                sd[p + f"mlp.e{e}.up"] = _t(seed, p + f"e{e}u", (Fn, W), 2.0 * s(W))
+                sd[p + f"mlp.e{e}.down"] = _t(seed, p + f"e{e}d", (W, Fn), s(Fn))
+    return sd
