@@ -74,8 +74,31 @@ def risepel_stack(width, layers, ff=None, window=512, pattern=("gla", "latent", 
                      logit_softcap=30.0)
 
 
+def lurepel_stack(width, layers, ff=None, chunk=1024, experts=16, identity=2, top=4, vocab=32768, compute_f32=False):
+    """A Lurepel-design stack at sizes that resemble a served model's layers (random-init benchmarks): heads of 128 channels,
+    four query heads per key/value head, half of each head rotated, attention inside blocks of `chunk` positions; layers
+    alternate a dense gated feed-forward of size ff with a mixture of `experts` experts of size ff / top (+ identity outputs)
+    of which every token uses `top`, so both kinds spend the same products per token."""
+    from . import engine as E
+    heads = max(1, width // 128)
+    ff = ff or (width * 4)
+    flags = E.ATTN_QK_UNIT_NORM | E.ATTN_V_IS_K | E.ATTN_UNIT_SINK | E.ATTN_HEAD_GATE
+    out = []
+    for i in range(layers):
+        l = E.LayerDesc(mixer=E.MIXER_GQA, heads=heads, kv_heads=max(1, heads // 4), dim=128, vdim=128, scale=128 ** -0.5,
+                        attn_flags=flags, mask=E.MASK_CHUNK, window=chunk, rope_dims=64, rope_pairing=1, rope_base=250000.0,
+                        rope_factor=8.0, rope_low=1.0, rope_high=4.0, rope_original=2048)
+        if i % 2 == 0:
+            l.ff_kind, l.ff = E.FF_GELU_TANH, ff
+        else:
+            l.ff_kind, l.ff, l.experts, l.identity_experts, l.top_k = E.FF_MOE, max(64, ff // top), experts, identity, top
+        out.append(l)
+    return E.StackDesc(width=width, vocab=vocab, layers=out, compute_f32=int(compute_f32), norm_eps=1e-5, resid_alpha=1.0,
+                       logit_softcap=0.0, norm_place=E.NORM_OF_OUTPUT, embed_norm=1, plain_gains=1)
+
+
 def llama_like(width, layers, ff, vocab=32768):
-    """The closest existing decoder at equal width / depth / feed-forward size (comparison arm of the Risepel benchmark)."""
+    """The closest existing decoder at equal width / depth / feed-forward size (comparison arm of the layer-list benchmarks)."""
     heads = max(1, width // 128)
     return ModelDesc(arch=LLAMA, hidden=width, layers=layers, heads=heads, kv_heads=max(1, heads // 4), head_dim=128, ffn=ff,
                      vocab=vocab, max_pos=8192, tie_embeddings=0, norm_eps=1e-5, rope_theta=500000.0)

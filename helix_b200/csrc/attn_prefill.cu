@@ -108,7 +108,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     bf16* __restrict__ out, int ldo,
                     const int32_t* __restrict__ cu_seqlens, int B, int Hq, int group, int causal, float scale_log2,
                     int max_q_pairs, const int32_t* __restrict__ kv_lens, const int32_t* __restrict__ page_table,
-                    int max_pages, int Hkv) {
+                    int max_pages, int Hkv, int chunk, int sink) {
   using C = ACfg<D>;
   constexpr int KST = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -136,6 +136,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   struct Item {
     int b, h, kvh, q0, seq0, len, kv_len, q_off, n0, n1, n;
+    int j_lo;  // first kv tile of the item (block mask: the tile that holds the block start of the pair's first row)
     bool valid, act1;
   };
   auto get_item = [&](int idx) {
@@ -155,8 +156,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int kv_tiles = (it.kv_len + BKV - 1) / BKV;
     it.act1 = it.q0 + BQ < it.len;
     // causal: q tile t needs kv tiles up to the one holding its last row's own position
-    it.n0 = causal ? min(kv_tiles, (it.q_off + it.q0 + BQ - 1) / BKV + 1) : kv_tiles;
-    it.n1 = it.act1 ? (causal ? min(kv_tiles, (it.q_off + it.q0 + 2 * BQ - 1) / BKV + 1) : kv_tiles) : 0;
+    // block mask (chunk > 0, paged only): a row sees its own block of `chunk` positions, counted from position 0, up to
+    // itself; tiles before the block of the pair's first row are skipped, n0 / n1 / n count tiles from j_lo
+    it.j_lo = (PAGED && chunk > 0) ? ((it.q_off + it.q0) / chunk * chunk) / BKV : 0;
+    it.n0 = (causal ? min(kv_tiles, (it.q_off + it.q0 + BQ - 1) / BKV + 1) : kv_tiles) - it.j_lo;
+    it.n1 = it.act1 ? (causal ? min(kv_tiles, (it.q_off + it.q0 + 2 * BQ - 1) / BKV + 1) : kv_tiles) - it.j_lo : 0;
     it.n = max(it.n0, it.n1);
     return it;
   };
@@ -217,7 +221,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           const int s = kt % KST;
           const uint32_t ph = (kt / KST) & 1;
           int blk = 0;  // PAGED: (page, kv head) block of the tile's page
-          if constexpr (PAGED) blk = page_table[(size_t)it.b * max_pages + j] * Hkv + it.kvh;
+          if constexpr (PAGED) blk = page_table[(size_t)it.b * max_pages + it.j_lo + j] * Hkv + it.kvh;
           mbar_wait(&k_empty[s], ph ^ 1);
           if (leader) {
             mbar_arrive_expect_tx(&k_full[s], C::KV_BYTES);
@@ -371,8 +375,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         mbar_wait(&s_full[t * 2 + (tile & 1)], (tile >> 1) & 1);
         tc_fence_after();
         if (t == 0 && warp == 3 && lane == 0) HB_TRACE(3);  // got S0(j)
-        const int kv0 = j * BKV;
-        const bool need_mask = (kv0 + BKV > len) || (causal && (kv0 + BKV - 1 > qt0));
+        const int kv0 = (it.j_lo + j) * BKV;
+        const int lo = chunk > 0 ? qpos / chunk * chunk : 0;     // first kv position this row sees
+        const bool need_mask = (kv0 + BKV > len) || (causal && (kv0 + BKV - 1 > qt0)) ||
+                               (chunk > 0 && kv0 < (qt0 + BQ - 1) / chunk * chunk);
         const int lim = causal ? min(len - 1, qpos) : len - 1;  // last valid kv position for this row
         // ---- the S row: back-to-back TMEM loads, ONE wait, then max / exp2 / pack entirely in registers
         uint32_t sv[BKV];
@@ -384,7 +390,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         tmem_ld_wait();
         if (need_mask) {  // diagonal / ragged tiles only: knock the invalid columns out once, the hot loops stay branch-free
 #pragma unroll
-          for (int i = 0; i < BKV; ++i) sv[i] = (kv0 + i <= lim) ? sv[i] : 0xff800000u;  // -inf
+          for (int i = 0; i < BKV; ++i) sv[i] = (kv0 + i <= lim && kv0 + i >= lo) ? sv[i] : 0xff800000u;  // -inf
         }
         float mx8[8];  // eight independent chains instead of one long dependent FMNMX chain
 #pragma unroll
@@ -458,6 +464,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // ---- item epilogue: O / l -> global, then hand O_t back to the MMA issuer
       mbar_wait(&pv_done[t * 2 + ((jt + nt - 1) & 1)], ((jt + nt - 1) >> 1) & 1);
       tc_fence_after();
+      if (sink) l += fast_exp2(-m_used);  // one more unit in the denominator: a key of score 0 that carries no value
       const float inv_l = l > 0.f ? 1.0f / l : 0.f;
       bool staged = false;
       if constexpr (C::STAGE_O) {
@@ -536,6 +543,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   }
 }
 
+inline int paged_only(int v, bool paged) { return paged ? v : 0; }
 template <int D, bool PAGED, int POLY>
 cudaError_t launch_p(cudaStream_t stream, const AttnPrefillArgs& a) {
   using C = ACfg<D>;
@@ -563,7 +571,8 @@ cudaError_t launch_p(cudaStream_t stream, const AttnPrefillArgs& a) {
   const int grid = (int)std::min<long long>(items, effective_sms(num_sms));  // hb_engine_cfg.sm_budget
   const float scale_log2 = a.scale * 1.4426950408889634f;
   kern<<<grid, kThreads, C::SMEM, stream>>>(mq, mk, mv, mo, a.out, a.ldo, a.cu_seqlens, a.B, a.Hq, a.Hq / a.Hkv, a.causal,
-                                            scale_log2, max_q_pairs, a.kv_lens, a.page_table, a.max_pages, a.Hkv);
+                                            scale_log2, max_q_pairs, a.kv_lens, a.page_table, a.max_pages, a.Hkv,
+                                            paged_only(a.block_mask, PAGED), a.unit_sink);
   return cudaGetLastError();
 }
 
@@ -633,8 +642,9 @@ cudaError_t attn_prefill_init() {
 cudaError_t attn_prefill(cudaStream_t stream, const AttnPrefillArgs& a) {
   if (a.B <= 0 || a.T <= 0) return cudaSuccess;
   if (a.Hq % a.Hkv) return cudaErrorInvalidValue;
-  if ((a.ldq % 8) || (a.ldk % 8) || (a.ldv % 8) || (a.ldo % 8)) return cudaErrorInvalidValue;
   const bool paged = a.k_cache != nullptr;
+  if ((a.ldq % 8) || (a.ldo % 8) || (!paged && ((a.ldk % 8) || (a.ldv % 8)))) return cudaErrorInvalidValue;
+  if (a.block_mask < 0 || (a.block_mask > 0 && (!paged || !a.causal))) return cudaErrorInvalidValue;
   if (paged) {
     if (!a.v_cache || !a.page_table || !a.kv_lens || a.max_pages <= 0 || a.num_pages <= 0 || a.page_size != 64) return cudaErrorInvalidValue;
     if (a.D == 128) return launch<128, true>(stream, a);

@@ -200,6 +200,13 @@ class Engine {
     float *moe_z = nullptr, *moe_w = nullptr, *moe_y = nullptr;
     int32_t* moe_ids = nullptr;
     int ldz = 0;
+    bf16* att16 = nullptr;  // grouped-query layers, bf16 mode: output of the fused tcgen05 attention [T][heads * vdim]
+    int ldatt = 0;
+    // experts as grouped tensor-core products (bf16 mode): items sorted by expert into a row buffer of moe_rows rows
+    int moe_rows = 0;
+    int32_t *moe_row_of = nullptr, *moe_src = nullptr, *moe_tiles = nullptr;
+    bf16 *moe_a16 = nullptr, *moe_h16 = nullptr;
+    float* moe_gu = nullptr;
     std::vector<const double*> freqs;  // per layer: rotation frequencies of a grouped-query layer (device), else null
   } sk_{};
   struct StepEntry { int t0, first, n; };  // host copy of the step's entries: first packed row, first position, tokens

@@ -175,8 +175,24 @@ static bool stack_att_caps(const Model& m, int* qb, size_t* rows, size_t* keys, 
 struct StackDims {
   int n1 = 0, n2 = 0, q = 0, qa = 0, cx = 0, mo = 0;
   int moe_r = 0, moe_top = 0, rope_half = 0;
+  int att = 0;               // grouped-query layers the fused tcgen05 attention takes: widest heads * vdim
+  int moe_e = 0, moe_f = 0;  // grouped tensor-core experts: most experts / widest expert over the layers that qualify
 };
-static StackDims stack_dims(const Model& m) {
+// Grouped-query layers whose prompt portions run on the fused tcgen05 attention kernel (the one the Llama path uses, with
+// the block mask and the unit of the denominator as parameters): bf16 mode, its head sizes, the pool's 64-position pages, and
+// a block or causal mask (a window that slides is left to the per-token kernel).
+static bool gqa_fused_ok(const Model& m, const hb_layer_desc& l, int max_ctx) {
+  static const bool off = [] { const char* e = getenv("HB_STACK_FUSED_ATTN"); return e && atoi(e) == 0; }();
+  return !off && !m.sd.compute_f32 && l.mixer == HB_MIXER_GQA && l.dim == l.vdim && (l.dim == 64 || l.dim == 128) &&
+         (l.mask == HB_MASK_CHUNK || l.window >= max_ctx);
+}
+// experts run as grouped tcgen05 products when the mode and the shapes allow (16-byte TMA strides, at least one MMA tile)
+static bool moe_grouped_ok(const Model& m, const hb_layer_desc& l) {
+  static const bool off = [] { const char* e = getenv("HB_STACK_MOE_GROUPED"); return e && atoi(e) == 0; }();
+  return !off && !m.sd.compute_f32 && l.ff > 0 && l.ff_kind == HB_FF_MOE && m.sd.width % 8 == 0 && l.ff % 8 == 0 && m.sd.width >= 64 &&
+         l.ff >= 64;
+}
+static StackDims stack_dims(const Model& m, int max_ctx) {
   StackDims d;
   for (int i = 0; i < m.sd.n_layers; ++i) {
     const hb_layer_desc& l = m.sl[i];
@@ -188,6 +204,7 @@ static StackDims stack_dims(const Model& m) {
     } else if (l.mixer == HB_MIXER_GQA) {
       d.n2 = std::max(d.n2, l.heads * l.dim);
       d.rope_half += l.rope_dims / 2;
+      if (gqa_fused_ok(m, l, max_ctx)) d.att = std::max(d.att, l.heads * l.vdim);
     } else {
       d.n2 = std::max(d.n2, l.heads * (l.dim + l.rot_dim));
       d.q = std::max(d.q, l.q_rank);
@@ -197,6 +214,10 @@ static StackDims stack_dims(const Model& m) {
     if (l.ff > 0 && l.ff_kind == HB_FF_MOE) {
       d.moe_r = std::max(d.moe_r, l.experts + l.identity_experts);
       d.moe_top = std::max(d.moe_top, l.top_k);
+      if (moe_grouped_ok(m, l)) {
+        d.moe_e = std::max(d.moe_e, l.experts);
+        d.moe_f = std::max(d.moe_f, l.ff);
+      }
     }
   }
   return d;
@@ -205,12 +226,18 @@ static StackDims stack_dims(const Model& m) {
 size_t Engine::workspace_bytes_stack() const {
   const hb_stack_desc& sd = model_.sd;
   const size_t T = t_cap_, W = sd.width;
-  const StackDims dm = stack_dims(model_);
+  const StackDims dm = stack_dims(model_, cfg_.max_ctx);
   const int n1 = dm.n1, n2 = dm.n2, q = dm.q, qa = dm.qa, cx = dm.cx, mo = dm.mo;
   size_t b = 0;
   b += al256((size_t)std::max(dm.rope_half, 1) * 8);
-  if (dm.moe_r > 0)
-    b += al256(T * (size_t)up8(dm.moe_r) * 4) + 2 * al256(T * (size_t)dm.moe_top * 4) + al256(T * (size_t)dm.moe_top * W * 4);
+  if (dm.att > 0) b += al256(T * (size_t)up8(dm.att) * 2);
+  if (dm.moe_r > 0) {
+    const size_t rows = dm.moe_e > 0 ? (size_t)moe_group_max_rows((int)T * dm.moe_top, dm.moe_e) : T * (size_t)dm.moe_top;
+    b += al256(T * (size_t)up8(dm.moe_r) * 4) + 2 * al256(T * (size_t)dm.moe_top * 4) + al256(rows * W * 4);
+    if (dm.moe_e > 0)
+      b += al256(T * (size_t)dm.moe_top * 4) + al256(rows * 4) + al256(rows / 128 * 4) + al256(rows * W * 2) + al256(rows * dm.moe_f * 2) +
+           al256(rows * 2 * (size_t)dm.moe_f * 4);
+  }
   b += 2 * al256(T * W * 4) + al256(T * W * 2);                       // x, y, x16
   b += al256(T * (size_t)up8(n1) * 4) + al256(T * (size_t)up8(n2) * 4);  // p1, p2
   b += al256(T * (size_t)up8(q) * 4) + al256(T * (size_t)up8(q) * 2);     // cq, cq16
@@ -262,7 +289,7 @@ int Engine::alloc_runtime_stack() {
     return r;
   };
   const size_t T = t_cap_, W = sd.width;
-  const StackDims dm = stack_dims(model_);
+  const StackDims dm = stack_dims(model_, cfg_.max_ctx);
   const int n1 = dm.n1, n2 = dm.n2, q = dm.q, qa = dm.qa, cx = dm.cx, mo = dm.mo;
   {  // rotation frequencies of the grouped-query layers (double precision, formed on the host)
     double* fq = (double*)take((size_t)std::max(dm.rope_half, 1) * 8);
@@ -277,12 +304,26 @@ int Engine::alloc_runtime_stack() {
       at += f.size();
     }
   }
+  if (dm.att > 0) {
+    sk_.ldatt = up8(dm.att);
+    sk_.att16 = (bf16*)take(T * (size_t)sk_.ldatt * 2);
+  }
   if (dm.moe_r > 0) {
     sk_.ldz = up8(dm.moe_r);
     sk_.moe_z = (float*)take(T * (size_t)sk_.ldz * 4);
     sk_.moe_ids = (int32_t*)take(T * (size_t)dm.moe_top * 4);
     sk_.moe_w = (float*)take(T * (size_t)dm.moe_top * 4);
-    sk_.moe_y = (float*)take(T * (size_t)dm.moe_top * W * 4);
+    const size_t rows = dm.moe_e > 0 ? (size_t)moe_group_max_rows((int)T * dm.moe_top, dm.moe_e) : T * (size_t)dm.moe_top;
+    sk_.moe_y = (float*)take(rows * W * 4);
+    if (dm.moe_e > 0) {
+      sk_.moe_rows = (int)rows;
+      sk_.moe_row_of = (int32_t*)take(T * (size_t)dm.moe_top * 4);
+      sk_.moe_src = (int32_t*)take(rows * 4);
+      sk_.moe_tiles = (int32_t*)take(rows / 128 * 4);
+      sk_.moe_a16 = (bf16*)take(rows * W * 2);
+      sk_.moe_h16 = (bf16*)take(rows * dm.moe_f * 2);
+      sk_.moe_gu = (float*)take(rows * 2 * (size_t)dm.moe_f * 4);
+    }
   }
   sk_.ld1 = up8(n1); sk_.ld2 = up8(n2); sk_.ldcq = up8(q); sk_.ldqa = up8(qa); sk_.ldctx = up8(cx); sk_.ldmo = up8(mo);
   sk_.x = (float*)take(T * W * 4);
@@ -466,13 +507,35 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       void* vplane = (uint8_t*)kv_ + plane_off_[w.cache_plane_v];
       GqaPrepArgs pa{};
       pa.p = k.p1; pa.ldp = k.ld1; pa.q_off = w.off_q; pa.k_off = w.off_k; pa.v_off = w.off_v;
-      pa.q = k.p2; pa.ldq = H * Dk; pa.q_b16 = nullptr;
+      // prompt portions (any entry of >= kAttDenseMin tokens): the whole step runs on the fused tcgen05 kernel over the paged
+      // planes; steps of single tokens and short portions, other masks, head sizes and the exact mode take the per-token kernel
+      bool fused = gqa_fused_ok(model_, l, cfg_.max_ctx) && k.att16 && k.q16 && (H * Dk) % 8 == 0 && page_ == 64;
+      int longest = 0;
+      for (const StepEntry& en : step_entries_) longest = std::max(longest, en.n);
+      fused = fused && longest >= kAttDenseMin;
+      pa.q = k.p2; pa.ldq = H * Dk; pa.q_b16 = fused ? k.q16 : nullptr;
       pa.k_cache = kplane; pa.v_cache = vplane; pa.f32 = f32;
       pa.slots = slots; pa.positions = positions;
       pa.freqs = k.freqs[i]; pa.rope_dims = l.rope_dims; pa.pairing = l.rope_pairing;
       pa.H = H; pa.G = G; pa.D = Dk; pa.Dv = Dv; pa.page_size = page_;
       pa.unit_norm = (l.attn_flags & HB_ATTN_QK_UNIT_NORM) != 0; pa.eps = sd.norm_eps; pa.T = T;
       SPAN(3, 8.0 * T * (H + 2 * G) * Dk, gqa_prep(stream_, pa));
+      if (fused) {
+        AttnPrefillArgs fa{};
+        fa.q = k.q16; fa.ldq = H * Dk;
+        fa.k = nullptr; fa.ldk = 0; fa.v = nullptr; fa.ldv = 0;
+        fa.out = k.att16; fa.ldo = H * Dv;
+        fa.cu_seqlens = cu; fa.B = B; fa.T = T; fa.max_seqlen = longest;
+        fa.Hq = H; fa.Hkv = G; fa.D = Dk; fa.causal = 1; fa.scale = l.scale;
+        fa.k_cache = (const bf16*)kplane; fa.v_cache = (const bf16*)vplane;
+        fa.page_table = pt; fa.kv_lens = (const int32_t*)(d_step_ + L.ctx);
+        fa.max_pages = max_pages_per_seq_; fa.num_pages = num_pages_; fa.page_size = page_;
+        fa.block_mask = l.mask == HB_MASK_CHUNK ? l.window : 0;
+        fa.unit_sink = (l.attn_flags & HB_ATTN_UNIT_SINK) ? 1 : 0;
+        SPAN(1, 2.0 * T * H * (double)std::min(l.window, cfg_.max_ctx) * (Dk + Dv) * 0.5, attn_prefill(stream_, fa));
+        SPAN(3, 10.0 * T * H * Dv, head_gate_rows(stream_, k.att16, H * Dv, (l.attn_flags & HB_ATTN_HEAD_GATE) ? k.p1 + w.off_g : nullptr,
+                                                  k.ld1, k.mo, mo16, T, H, Dv));
+      } else {
       GqaAttnArgs aa{};
       aa.q = k.p2; aa.ldq = H * Dk;
       aa.k_cache = kplane; aa.v_cache = vplane; aa.f32 = f32;
@@ -483,6 +546,7 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       aa.T = T; aa.H = H; aa.G = G; aa.D = Dk; aa.Dv = Dv; aa.mask = l.mask; aa.window = l.window;
       aa.unit_sink = (l.attn_flags & HB_ATTN_UNIT_SINK) != 0; aa.scale = l.scale;
       SPAN(7, 2.0 * T * H * (double)std::min(l.window, cfg_.max_ctx) * (Dk + Dv), gqa_attn(stream_, aa));
+      }
     } else {
       const int R = l.kv_rank, Dr = l.rot_dim, Q = l.q_rank;
       uint8_t* plane = (uint8_t*)kv_ + plane_off_[w.cache_plane];
@@ -585,8 +649,24 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       GemmRtArgs g{k.x, W, 0, w.router, W, 1, 0, k.moe_z, k.ldz, 0, nullptr, T, R, W, 1, f32};
       SPAN(5, 2.0 * T * R * W, gemm_rt(stream_, g));
       SPAN(3, 8.0 * T * R, moe_route(stream_, k.moe_z, k.ldz, w.correction, f32, R, l.top_k, k.moe_ids, k.moe_w, T));
-      SPAN(5, 6.0 * T * l.top_k * F * W, moe_expert_rows(stream_, k.x, x16, w.w_gu, w.w_down, f32, k.moe_ids, l.top_k, E, F, W, k.moe_y, T));
-      SPAN(3, 4.0 * T * (l.top_k + 2) * W, moe_combine(stream_, k.x, k.moe_y, k.moe_ids, k.moe_w, l.top_k, E, k.y, T, W));
+      const int items = T * l.top_k;
+      if (moe_grouped_ok(model_, l) && k.moe_a16 && items >= 2 * E) {
+        // items sorted by expert into 128-row segments; both products of every expert in two grouped tcgen05 launches
+        const int rows = moe_group_max_rows(items, E);
+        SPAN(3, 12.0 * items, moe_group_rows(stream_, k.moe_ids, items, l.top_k, E, k.moe_row_of, k.moe_src, k.moe_tiles));
+        SPAN(3, 4.0 * rows * W, moe_gather_rows(stream_, x16, W, k.moe_src, k.moe_a16, rows));
+        GemmArgs g1{k.moe_a16, W, (const bf16*)w.w_gu, W, k.moe_gu, 2 * F, nullptr, 0, nullptr, rows, 2 * F, W, EPI_F32, 0};
+        g1.m_tile_group = k.moe_tiles; g1.groups = E;
+        SPAN(0, 4.0 * rows * F * W, gemm_bf16_tn(stream_, g1));
+        SPAN(3, 10.0 * rows * F, gated_unit(stream_, k.moe_gu, 2 * F, GLU_SILU, nullptr, k.moe_h16, rows, F));
+        GemmArgs g2{k.moe_h16, F, (const bf16*)w.w_down, F, k.moe_y, W, nullptr, 0, nullptr, rows, W, F, EPI_F32, 0};
+        g2.m_tile_group = k.moe_tiles; g2.groups = E;
+        SPAN(0, 2.0 * rows * F * W, gemm_bf16_tn(stream_, g2));
+        SPAN(3, 4.0 * T * (l.top_k + 2) * W, moe_combine_rows(stream_, k.x, k.moe_y, k.moe_row_of, k.moe_w, l.top_k, k.y, T, W));
+      } else {
+        SPAN(5, 6.0 * items * F * W, moe_expert_rows(stream_, k.x, x16, w.w_gu, w.w_down, f32, k.moe_ids, l.top_k, E, F, W, k.moe_y, T));
+        SPAN(3, 4.0 * T * (l.top_k + 2) * W, moe_combine(stream_, k.x, k.moe_y, k.moe_ids, k.moe_w, l.top_k, E, k.y, T, W));
+      }
       SPAN(3, 3 * rowb, resid(nullptr, w.norm2));
     } else if (l.ff > 0 && l.ff_kind == HB_FF_GELU_TANH) {
       const int F = l.ff;

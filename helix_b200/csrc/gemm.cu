@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_r,
                const bf16* __restrict__ bias, int M, int N, int K, int tile_grp, int tile_group_n,
-               const __grid_constant__ RopeEpi rope) {
+               const __grid_constant__ RopeEpi rope, const int32_t* __restrict__ m_tile_group) {
   using C = Cfg<BN, CG>;
   constexpr int TILE_M = BLOCK_M * CG;  // rows of one UMMA tile (per CTA: BLOCK_M)
   const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
@@ -183,6 +183,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       for (int t = tile_worker; t < num_tiles; t += tile_workers) {
         int mi, ni;
         tile_coords(t, num_m, num_n, tile_grp, tile_group_n & 1, mi, ni);
+        // grouped weights (single-CTA tiles only): the rows of m tile mi multiply the N weight rows of its group
+        const int w_row0 = (m_tile_group ? __ldg(m_tile_group + mi) * N : 0) + ni * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
           mbar_wait(&empty_bar[s], phase ^ 1);
           if (elected) {
@@ -197,7 +199,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             } else {
               mbar_arrive_expect_tx(&full_bar[s], C::STAGE_BYTES);
               tma_load_2d(smem_a + s * C::A_BYTES, &map_a, &full_bar[s], kb * BLOCK_K, mi * BLOCK_M, hint_a);
-              tma_load_2d(smem_b + s * C::B_BYTES, &map_b, &full_bar[s], kb * BLOCK_K, ni * BN, hint_b);
+              tma_load_2d(smem_b + s * C::B_BYTES, &map_b, &full_bar[s], kb * BLOCK_K, w_row0, hint_b);
             }
           }
           if (++s == STAGES) { s = 0; phase ^= 1; }
@@ -473,7 +475,9 @@ cudaError_t launch_cfg(cudaStream_t stream, const GemmArgs& g, int num_sms) {
   CUtensorMap ma, mb, mc, mr;
   const int n_out = kSwiGLU ? g.N / 2 : g.N;
   if (!make_tmap_2d(&ma, g.A, TM_BF16, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda * 2, BLOCK_K, BLOCK_M)) return cudaErrorInvalidValue;
-  if (!make_tmap_2d(&mb, g.W, TM_BF16, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldw * 2, BLOCK_K, BN / CG)) return cudaErrorInvalidValue;
+  if (CG != 1 && g.m_tile_group) return cudaErrorInvalidValue;
+  const uint64_t w_rows = (uint64_t)g.N * (g.m_tile_group ? std::max(1, g.groups) : 1);
+  if (!make_tmap_2d(&mb, g.W, TM_BF16, (uint64_t)g.K, w_rows, (uint64_t)g.ldw * 2, BLOCK_K, BN / CG)) return cudaErrorInvalidValue;
   if (kF32) {
     if (!make_tmap_2d(&mc, g.C, TM_F32, (uint64_t)n_out, (uint64_t)g.M, (uint64_t)g.ldc * 4, 32, BLOCK_M)) return cudaErrorInvalidValue;
   } else {
@@ -518,7 +522,7 @@ cudaError_t launch_cfg(cudaStream_t stream, const GemmArgs& g, int num_sms) {
   cfg.attrs = attr;
   cfg.numAttrs = (CG > 1) ? 1 : 0;
   static const int l2_hints = [] { const char* e = getenv("HB_GEMM_L2HINTS"); return e ? atoi(e) : 0; }();  // A/B knob
-  return cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, mr, g.bias, g.M, g.N, g.K, grp, group_n | (l2_hints ? 2 : 0), g.rope);
+  return cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, mr, g.bias, g.M, g.N, g.K, grp, group_n | (l2_hints ? 2 : 0), g.rope, g.m_tile_group);
 }
 
 bool use_pair() {  // HB_GEMM_2CTA=0 falls back to single-CTA tiles (A/B measurements)
@@ -538,7 +542,7 @@ cudaError_t launch_epi(cudaStream_t stream, const GemmArgs& g, int num_sms) {
   switch (bn) {
     case 256:
       // CTA pairs (256 x 256 tiles) once the problem has at least a wave of them
-      if (use_pair() && (long)((g.M + 255) / 256) * ((g.N + 255) / 256) >= num_sms / 2) return launch_cfg<256, EPI, 2>(stream, g, num_sms);
+      if (use_pair() && !g.m_tile_group && (long)((g.M + 255) / 256) * ((g.N + 255) / 256) >= num_sms / 2) return launch_cfg<256, EPI, 2>(stream, g, num_sms);
       return launch_cfg<256, EPI, 1>(stream, g, num_sms);
     case 128:
       if constexpr (EPI != EPI_SWIGLU && EPI != EPI_ROPE) return launch_cfg<128, EPI, 1>(stream, g, num_sms);

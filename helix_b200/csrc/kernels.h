@@ -55,6 +55,10 @@ struct GemmArgs {
   Epi epi;
   int block_n;  // 0 = choose
   RopeEpi rope{};  // EPI_ROPE only
+  // Grouped weights (mixtures of experts): W holds `groups` matrices of N rows each, one after the other; the 128 rows of m
+  // tile i of A multiply the matrix m_tile_group[i] (device array, ceil(M / 128) entries, every entry a valid group).
+  const int32_t* m_tile_group = nullptr;
+  int groups = 1;
 };
 cudaError_t gemm_bf16_tn(cudaStream_t stream, const GemmArgs& a);
 // Debug/test-only CUDA-core GEMM (same contract, EPI_NONE/EPI_F32 only); used by tests as an on-device checker.
@@ -117,6 +121,10 @@ struct AttnPrefillArgs {
   const int32_t* page_table = nullptr;  // [B, max_pages]
   const int32_t* kv_lens = nullptr;     // [B] kv length including this step's q rows
   int max_pages = 0, num_pages = 0, page_size = 64;
+  // paged + causal only.  block_mask > 0: a position sees only the keys of its own block of block_mask positions (blocks
+  // counted from position 0 of the sequence).  unit_sink: one unit added to the softmax denominator (a key of score 0 that
+  // carries no value)
+  int block_mask = 0, unit_sink = 0;
 };
 cudaError_t attn_prefill(cudaStream_t stream, const AttnPrefillArgs& a);
 // test-only CUDA-core checker, fp32 output [T, ldo]
@@ -378,11 +386,14 @@ struct GqaAttnArgs {
 };
 cudaError_t gqa_attn(cudaStream_t s, const GqaAttnArgs& a);
 size_t gqa_attn_smem(int D, int Dv, int max_keys);  // dynamic shared memory the kernel needs to see max_keys keys
+// out[t, h*Dv + i] = o[t, h*Dv + i] * sigmoid(gate[t, h])  (gate null: copy), o in bf16, out as fp32 + bf16 copy
+cudaError_t head_gate_rows(cudaStream_t s, const bf16* o, long ldo, const float* gate, long ldg, float* out, bf16* out_b16, int T, int H,
+                           int Dv);
 
 // ---- gated feed-forward units and mixtures of experts (stack_moe.cu).
 cudaError_t stack_moe_init();
 enum GluAct : int { GLU_SILU = 0, GLU_GELU_TANH = 1 };
-// out[t, j] = act(gu[t, j]) * gu[t, F + j]   (row stride ldg)
+// out[t, j] = act(gu[t, j]) * gu[t, F + j]   (row stride ldg; out may be null when only the bf16 copy is wanted)
 cudaError_t gated_unit(cudaStream_t s, const float* gu, long ldg, int act, float* out, bf16* out_b16, int T, int F);
 // Router: scores = softmax(z[t, :R]) in fp32; the top_k largest of (score + correction) are chosen, lowest index first among
 // equals; ids[t, k] = chosen output, wts[t, k] = its score (not renormalised)
@@ -393,6 +404,17 @@ cudaError_t moe_route(cudaStream_t s, const float* z, long ldz, const void* corr
 // activation to bf16, as the tensor-core path does.  w_gu: [E][2F][W] ([gate | up] rows), w_down: [E][W][F].
 cudaError_t moe_expert_rows(cudaStream_t s, const float* x, const bf16* x_b16, const void* w_gu, const void* w_down, bool f32,
                             const int32_t* ids, int top_k, int E, int F, int W, float* y, int T);
+// The same experts as grouped tensor-core products (bf16 mode): moe_group_rows sorts the (token, choice) items by expert into
+// a row buffer of moe_group_max_rows(items, E) rows whose per-expert segments start on multiples of 128 rows (row_of[item] =
+// its row or -1 for an identity output, src_of_row[row] = its token or -1, tile_group[row / 128] = the expert whose weights
+// multiply that m tile — GemmArgs::m_tile_group); moe_gather_rows copies the tokens' bf16 rows into it (zeros elsewhere);
+// moe_combine_rows is moe_combine over the row buffer.
+int moe_group_max_rows(int n_items, int E);
+cudaError_t moe_group_rows(cudaStream_t s, const int32_t* ids, int n_items, int top_k, int E, int32_t* row_of, int32_t* src_of_row,
+                           int32_t* tile_group);
+cudaError_t moe_gather_rows(cudaStream_t s, const bf16* x16, int W, const int32_t* src_of_row, bf16* a16, int rows);
+cudaError_t moe_combine_rows(cudaStream_t s, const float* x, const float* y, const int32_t* row_of, const float* wts, int top_k,
+                             float* out, int T, int W);
 // out[t, :] = sum_k wts[t, k] * (ids[t, k] < E ? y[(t, k), :] : x[t, :]), k in order
 cudaError_t moe_combine(cudaStream_t s, const float* x, const float* y, const int32_t* ids, const float* wts, int top_k, int E,
                         float* out, int T, int W);

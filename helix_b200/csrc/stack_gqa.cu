@@ -253,7 +253,25 @@ __global__ void __launch_bounds__(kAttThreads) gqa_attn_kernel(GqaAttnArgs a, in
   }
 }
 
+__global__ void head_gate_kernel(const bf16* __restrict__ o, long ldo, const float* __restrict__ gate, long ldg, float* __restrict__ out,
+                                 bf16* __restrict__ outb, int H, int Dv) {
+  const size_t t = blockIdx.x;
+  for (int e = threadIdx.x; e < H * Dv; e += blockDim.x) {
+    const float g = gate ? sigmoidf_(gate[t * ldg + e / Dv]) : 1.f;
+    const float v = __bfloat162float(o[t * ldo + e]) * g;
+    out[t * H * Dv + e] = v;
+    if (outb) outb[t * H * Dv + e] = __float2bfloat16(v);
+  }
+}
+
 }  // namespace
+
+cudaError_t head_gate_rows(cudaStream_t s, const bf16* o, long ldo, const float* gate, long ldg, float* out, bf16* outb, int T, int H,
+                           int Dv) {
+  if (T <= 0) return cudaSuccess;
+  head_gate_kernel<<<T, 256, 0, s>>>(o, ldo, gate, ldg, out, outb, H, Dv);
+  return cudaGetLastError();
+}
 
 size_t gqa_attn_smem(int D, int Dv, int max_keys) {
   (void)Dv;

@@ -18,14 +18,14 @@ __device__ __forceinline__ float glu_act(float z, int act) { return act == GLU_G
 // VEC = 4: F and ldg are multiples of four (16-byte loads and stores)
 template <int VEC>
 __global__ void gated_unit_kernel(const float* __restrict__ gu, long ldg, int act, float* __restrict__ out, bf16* __restrict__ outb, int F) {
-  const int t = blockIdx.x;
+  const size_t t = blockIdx.x;
   const int j = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
   if (j >= F) return;
   if (VEC == 4) {
     const float4 g = *reinterpret_cast<const float4*>(gu + (size_t)t * ldg + j);
     const float4 u = *reinterpret_cast<const float4*>(gu + (size_t)t * ldg + F + j);
     const float v0 = glu_act(g.x, act) * u.x, v1 = glu_act(g.y, act) * u.y, v2 = glu_act(g.z, act) * u.z, v3 = glu_act(g.w, act) * u.w;
-    *reinterpret_cast<float4*>(out + (size_t)t * F + j) = make_float4(v0, v1, v2, v3);
+    if (out) *reinterpret_cast<float4*>(out + (size_t)t * F + j) = make_float4(v0, v1, v2, v3);
     if (outb) {
       __nv_bfloat162 lo = __floats2bfloat162_rn(v0, v1), hi = __floats2bfloat162_rn(v2, v3);
       uint2 pk;
@@ -35,7 +35,7 @@ __global__ void gated_unit_kernel(const float* __restrict__ gu, long ldg, int ac
     }
   } else {
     const float v = glu_act(gu[(size_t)t * ldg + j], act) * gu[(size_t)t * ldg + F + j];
-    out[(size_t)t * F + j] = v;
+    if (out) out[(size_t)t * F + j] = v;
     if (outb) outb[(size_t)t * F + j] = __float2bfloat16(v);
   }
 }
@@ -150,7 +150,99 @@ __global__ void moe_combine_kernel(const float* __restrict__ x, const float* __r
   }
 }
 
+// Groups the (token, choice) items by expert for the grouped tensor-core products.  One block.  Expert e's items get the rows
+// [off_e, off_e + count_e) of a row buffer whose per-expert segments start on multiples of 128 rows (one m tile never mixes
+// experts); rows between segments and behind the last one stay empty (src -1) and belong to expert 0's tiles, so every tile
+// of the buffer can be multiplied without the host knowing the counts.  Which row of its segment an item gets depends on
+// arrival order; a row's product does not depend on where the row sits.
+__global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t* __restrict__ ids, int n_items, int top_k, int E, int max_rows,
+                                                         int32_t* __restrict__ row_of, int32_t* __restrict__ src_of_row,
+                                                         int32_t* __restrict__ tile_group) {
+  extern __shared__ int smi[];
+  int* cnt = smi;
+  int* off = smi + E;
+  int* cur = smi + 2 * E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_items; i += blockDim.x) {
+    const int e = ids[i];
+    if (e < E) atomicAdd(&cnt[e], 1);
+  }
+  for (int r = threadIdx.x; r < max_rows; r += blockDim.x) src_of_row[r] = -1;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0;
+    for (int e = 0; e < E; ++e) {
+      off[e] = o;
+      cur[e] = 0;
+      const int nt = (cnt[e] + 127) / 128;
+      for (int k = 0; k < nt; ++k) tile_group[o / 128 + k] = e;
+      o += nt * 128;
+    }
+    for (int tl = o / 128; tl < max_rows / 128; ++tl) tile_group[tl] = 0;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_items; i += blockDim.x) {
+    const int e = ids[i];
+    int r = -1;
+    if (e < E) {
+      r = off[e] + atomicAdd(&cur[e], 1);
+      src_of_row[r] = i / top_k;
+    }
+    row_of[i] = r;
+  }
+}
+
+// a16[r, :] = x16[src_of_row[r], :], zeros for empty rows.  W is a multiple of 8 (16-byte pieces)
+__global__ void __launch_bounds__(128) moe_gather_kernel(const bf16* __restrict__ x16, int W, const int32_t* __restrict__ src_of_row,
+                                                         bf16* __restrict__ a16) {
+  const size_t r = blockIdx.x;
+  const int src = src_of_row[r];
+  uint4* dst = reinterpret_cast<uint4*>(a16 + r * W);
+  const uint4* from = reinterpret_cast<const uint4*>(x16 + (size_t)(src < 0 ? 0 : src) * W);
+  for (int i = threadIdx.x; i < W / 8; i += blockDim.x) dst[i] = src < 0 ? make_uint4(0, 0, 0, 0) : from[i];
+}
+
+__global__ void moe_combine_rows_kernel(const float* __restrict__ x, const float* __restrict__ y, const int32_t* __restrict__ row_of,
+                                        const float* __restrict__ wts, int top_k, float* __restrict__ out, int W) {
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top_k; ++k) {
+      const size_t item = (size_t)t * top_k + k;
+      const int r = row_of[item];
+      const float v = r >= 0 ? y[(size_t)r * W + c] : x[(size_t)t * W + c];
+      acc = fmaf(wts[item], v, acc);
+    }
+    out[(size_t)t * W + c] = acc;
+  }
+}
+
 }  // namespace
+
+int moe_group_max_rows(int n_items, int E) { return (n_items + 127) / 128 * 128 + E * 128; }
+
+cudaError_t moe_group_rows(cudaStream_t s, const int32_t* ids, int n_items, int top_k, int E, int32_t* row_of, int32_t* src_of_row,
+                           int32_t* tile_group) {
+  if (n_items <= 0) return cudaSuccess;
+  if (E > 4096) return cudaErrorInvalidValue;
+  moe_group_kernel<<<1, 1024, (size_t)3 * E * 4, s>>>(ids, n_items, top_k, E, moe_group_max_rows(n_items, E), row_of, src_of_row, tile_group);
+  return cudaGetLastError();
+}
+
+cudaError_t moe_gather_rows(cudaStream_t s, const bf16* x16, int W, const int32_t* src_of_row, bf16* a16, int rows) {
+  if (rows <= 0) return cudaSuccess;
+  if (W % 8) return cudaErrorInvalidValue;
+  moe_gather_kernel<<<rows, 128, 0, s>>>(x16, W, src_of_row, a16);
+  return cudaGetLastError();
+}
+
+cudaError_t moe_combine_rows(cudaStream_t s, const float* x, const float* y, const int32_t* row_of, const float* wts, int top_k,
+                             float* out, int T, int W) {
+  if (T <= 0) return cudaSuccess;
+  moe_combine_rows_kernel<<<T, 256, 0, s>>>(x, y, row_of, wts, top_k, out, W);
+  return cudaGetLastError();
+}
 
 cudaError_t stack_moe_init() {
   cudaError_t e;

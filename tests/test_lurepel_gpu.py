@@ -94,6 +94,9 @@ CONFIGS = {
     "one_expert_many_identities": dict(order=("moe",), identity=3, top=2, experts=1),
     "layers_differ": dict(order=("moe", "dense", "moe"), per_layer={0: dict(heads=2, kv_heads=1, dim=40, mask=dict(size=7)),
                                                                     2: dict(heads=8, kv_heads=4, dim=8, rot=dict(base=30.0, dims=4))}),
+    # head sizes of the fused tensor-core attention with blocks shorter than its 64-key tiles / longer than a page
+    "fused_attention_small_blocks": dict(width=128, heads=4, kv_heads=1, dim=64, rot_dims=64, chunk=20, order=("dense",)),
+    "fused_attention_128": dict(width=128, vocab=256, heads=2, kv_heads=2, dim=128, rot_dims=32, chunk=70, order=("dense", None)),
     "tensor_core_shapes": dict(width=128, vocab=256, heads=4, kv_heads=2, dim=64, rot_dims=32, chunk=96, ff=128, expert_ff=64),
 }
 
