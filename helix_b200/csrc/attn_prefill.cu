@@ -108,7 +108,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     bf16* __restrict__ out, int ldo,
                     const int32_t* __restrict__ cu_seqlens, int B, int Hq, int group, int causal, float scale_log2,
                     int max_q_pairs, const int32_t* __restrict__ kv_lens, const int32_t* __restrict__ page_table,
-                    int max_pages, int Hkv, int chunk, int sink) {
+                    int max_pages, int Hkv, int chunk, int sink, const float* __restrict__ head_gate, int ldg) {
   using C = ACfg<D>;
   constexpr int KST = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -465,7 +465,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       mbar_wait(&pv_done[t * 2 + ((jt + nt - 1) & 1)], ((jt + nt - 1) >> 1) & 1);
       tc_fence_after();
       if (sink) l += fast_exp2(-m_used);  // one more unit in the denominator: a key of score 0 that carries no value
-      const float inv_l = l > 0.f ? 1.0f / l : 0.f;
+      float inv_l = l > 0.f ? 1.0f / l : 0.f;
+      // optional output gate: the head's rows are scaled by sigmoid(head_gate[token][head]) on their way out
+      if (head_gate != nullptr && qrow < it.len) inv_l *= 1.f / (1.f + __expf(-head_gate[(size_t)(it.seq0 + qrow) * ldg + it.h]));
       bool staged = false;
       if constexpr (C::STAGE_O) {
         // Every thread writing its own 128-byte row straight to global is 32 distinct lines per store instruction: ncu
@@ -572,7 +574,7 @@ cudaError_t launch_p(cudaStream_t stream, const AttnPrefillArgs& a) {
   const float scale_log2 = a.scale * 1.4426950408889634f;
   kern<<<grid, kThreads, C::SMEM, stream>>>(mq, mk, mv, mo, a.out, a.ldo, a.cu_seqlens, a.B, a.Hq, a.Hq / a.Hkv, a.causal,
                                             scale_log2, max_q_pairs, a.kv_lens, a.page_table, a.max_pages, a.Hkv,
-                                            paged_only(a.block_mask, PAGED), a.unit_sink);
+                                            paged_only(a.block_mask, PAGED), a.unit_sink, a.head_gate, a.ldg);
   return cudaGetLastError();
 }
 

@@ -119,6 +119,7 @@ class Engine {
   int alloc_runtime_stack();
   // one step over T packed tokens of B entries; logits of the entries' last rows -> logits_ (+ sampling when `sample`);
   // n_extra > 0: logits of rows extra_rows[0..n_extra) (device indices; null = rows 0..n_extra-1) -> extra_out
+  bool stack_tc(int N, int K, int lda, int ldc) const;  // stack_gemm takes a tensor-core path for this shape at any M
   int forward_stack(int T, int B, const StepLayout& L, const int32_t* extra_rows, int n_extra, float* extra_out, bool sample);
   // C[M, N] (fp32, row stride ldc) = A . W^T: tcgen05 GEMM when the mode and the strides allow it (A_b16 = bf16 copy of A),
   // CUDA-core fp32 GEMM otherwise
@@ -206,7 +207,7 @@ class Engine {
     int moe_rows = 0;
     int32_t *moe_row_of = nullptr, *moe_src = nullptr, *moe_tiles = nullptr;
     bf16 *moe_a16 = nullptr, *moe_h16 = nullptr;
-    float* moe_gu = nullptr;
+    bf16* gu16 = nullptr;  // [gate | up] products of a gated unit as bf16 (tensor-core path of steps of > 256 tokens, experts)
     std::vector<const double*> freqs;  // per layer: rotation frequencies of a grouped-query layer (device), else null
   } sk_{};
   struct StepEntry { int t0, first, n; };  // host copy of the step's entries: first packed row, first position, tokens

@@ -175,6 +175,7 @@ static bool stack_att_caps(const Model& m, int* qb, size_t* rows, size_t* keys, 
 struct StackDims {
   int n1 = 0, n2 = 0, q = 0, qa = 0, cx = 0, mo = 0;
   int moe_r = 0, moe_top = 0, rope_half = 0;
+  int gu = 0;                // widest [gate | up] row of a plain gated unit (bf16 intermediate of the tensor-core path)
   int att = 0;               // grouped-query layers the fused tcgen05 attention takes: widest heads * vdim
   int moe_e = 0, moe_f = 0;  // grouped tensor-core experts: most experts / widest expert over the layers that qualify
 };
@@ -211,6 +212,7 @@ static StackDims stack_dims(const Model& m, int max_ctx) {
       d.qa = std::max(d.qa, l.heads * (l.kv_rank + l.rot_dim));
       d.cx = std::max(d.cx, std::max(l.heads * l.kv_rank, l.heads * l.vdim));
     }
+    if (l.ff > 0 && l.ff_kind == HB_FF_GELU_TANH) d.gu = std::max(d.gu, 2 * l.ff);
     if (l.ff > 0 && l.ff_kind == HB_FF_MOE) {
       d.moe_r = std::max(d.moe_r, l.experts + l.identity_experts);
       d.moe_top = std::max(d.moe_top, l.top_k);
@@ -235,8 +237,11 @@ size_t Engine::workspace_bytes_stack() const {
     const size_t rows = dm.moe_e > 0 ? (size_t)moe_group_max_rows((int)T * dm.moe_top, dm.moe_e) : T * (size_t)dm.moe_top;
     b += al256(T * (size_t)up8(dm.moe_r) * 4) + 2 * al256(T * (size_t)dm.moe_top * 4) + al256(rows * W * 4);
     if (dm.moe_e > 0)
-      b += al256(T * (size_t)dm.moe_top * 4) + al256(rows * 4) + al256(rows / 128 * 4) + al256(rows * W * 2) + al256(rows * dm.moe_f * 2) +
-           al256(rows * 2 * (size_t)dm.moe_f * 4);
+      b += al256(T * (size_t)dm.moe_top * 4) + al256(rows * 4) + al256(rows / 128 * 4) + al256(rows * W * 2) + al256(rows * dm.moe_f * 2);
+  }
+  if (!sd.compute_f32) {
+    const size_t rows = dm.moe_e > 0 ? (size_t)moe_group_max_rows((int)T * dm.moe_top, dm.moe_e) : 0;
+    b += al256(std::max(T * (size_t)up8(dm.gu), rows * 2 * (size_t)dm.moe_f) * 2 + 256);
   }
   b += 2 * al256(T * W * 4) + al256(T * W * 2);                       // x, y, x16
   b += al256(T * (size_t)up8(n1) * 4) + al256(T * (size_t)up8(n2) * 4);  // p1, p2
@@ -322,8 +327,11 @@ int Engine::alloc_runtime_stack() {
       sk_.moe_tiles = (int32_t*)take(rows / 128 * 4);
       sk_.moe_a16 = (bf16*)take(rows * W * 2);
       sk_.moe_h16 = (bf16*)take(rows * dm.moe_f * 2);
-      sk_.moe_gu = (float*)take(rows * 2 * (size_t)dm.moe_f * 4);
     }
+  }
+  if (!sd.compute_f32) {
+    const size_t rows = dm.moe_e > 0 ? (size_t)moe_group_max_rows((int)T * dm.moe_top, dm.moe_e) : 0;
+    sk_.gu16 = (bf16*)take(std::max(T * (size_t)up8(dm.gu), rows * 2 * (size_t)dm.moe_f) * 2 + 256);
   }
   sk_.ld1 = up8(n1); sk_.ld2 = up8(n2); sk_.ldcq = up8(q); sk_.ldqa = up8(qa); sk_.ldctx = up8(cx); sk_.ldmo = up8(mo);
   sk_.x = (float*)take(T * W * 4);
@@ -425,6 +433,11 @@ void Engine::drop_slot(Request* r) {
 }
 
 // ------------------------------------------------------------------ forward
+bool Engine::stack_tc(int N, int K, int lda, int ldc) const {
+  static const bool simt_only = [] { const char* e = getenv("HB_STACK_SIMT"); return e && atoi(e) != 0; }();
+  return !model_.sd.compute_f32 && !simt_only && K % 8 == 0 && lda % 8 == 0 && K >= 64 && N >= 64 && ldc % 4 == 0;
+}
+
 int Engine::stack_gemm(const float* A, const bf16* A16, int lda, const void* Wt, int N, int K, float* C, int ldc, int M, const void* bias) {
   const bool f32 = model_.sd.compute_f32 != 0;
   static const bool simt_only = [] { const char* e = getenv("HB_STACK_SIMT"); return e && atoi(e) != 0; }();  // A/B and bring-up
@@ -524,7 +537,9 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
         AttnPrefillArgs fa{};
         fa.q = k.q16; fa.ldq = H * Dk;
         fa.k = nullptr; fa.ldk = 0; fa.v = nullptr; fa.ldv = 0;
-        fa.out = k.att16; fa.ldo = H * Dv;
+        const bool direct = stack_tc(W, H * Dv, H * Dv, W);  // the output projection reads the bf16 copy only
+        fa.out = direct ? mo16 : k.att16; fa.ldo = H * Dv;
+        if (direct && (l.attn_flags & HB_ATTN_HEAD_GATE)) { fa.head_gate = k.p1 + w.off_g; fa.ldg = k.ld1; }
         fa.cu_seqlens = cu; fa.B = B; fa.T = T; fa.max_seqlen = longest;
         fa.Hq = H; fa.Hkv = G; fa.D = Dk; fa.causal = 1; fa.scale = l.scale;
         fa.k_cache = (const bf16*)kplane; fa.v_cache = (const bf16*)vplane;
@@ -533,8 +548,9 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
         fa.block_mask = l.mask == HB_MASK_CHUNK ? l.window : 0;
         fa.unit_sink = (l.attn_flags & HB_ATTN_UNIT_SINK) ? 1 : 0;
         SPAN(1, 2.0 * T * H * (double)std::min(l.window, cfg_.max_ctx) * (Dk + Dv) * 0.5, attn_prefill(stream_, fa));
-        SPAN(3, 10.0 * T * H * Dv, head_gate_rows(stream_, k.att16, H * Dv, (l.attn_flags & HB_ATTN_HEAD_GATE) ? k.p1 + w.off_g : nullptr,
-                                                  k.ld1, k.mo, mo16, T, H, Dv));
+        if (!direct)
+          SPAN(3, 10.0 * T * H * Dv, head_gate_rows(stream_, k.att16, H * Dv, (l.attn_flags & HB_ATTN_HEAD_GATE) ? k.p1 + w.off_g : nullptr,
+                                                    k.ld1, k.mo, mo16, T, H, Dv));
       } else {
       GqaAttnArgs aa{};
       aa.q = k.p2; aa.ldq = H * Dk;
@@ -646,19 +662,24 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
     if (l.ff > 0 && l.ff_kind == HB_FF_MOE) {
       // router in fp32 on the stream itself; experts per (token, choice); identity outputs and weights in the combination
       const int E = l.experts, R = l.experts + l.identity_experts, F = l.ff;
-      GemmRtArgs g{k.x, W, 0, w.router, W, 1, 0, k.moe_z, k.ldz, 0, nullptr, T, R, W, 1, f32};
-      SPAN(5, 2.0 * T * R * W, gemm_rt(stream_, g));
-      SPAN(3, 8.0 * T * R, moe_route(stream_, k.moe_z, k.ldz, w.correction, f32, R, l.top_k, k.moe_ids, k.moe_w, T));
+      if (moe_router_smem(R, W, f32) <= 200 * 1024) {
+        SPAN(3, 4.0 * T * W, moe_router(stream_, k.x, w.router, w.correction, f32, R, W, l.top_k, k.moe_ids, k.moe_w, T,
+                                        cfg_.sm_budget > 0 ? cfg_.sm_budget : 148));
+      } else {  // a router too large for shared memory: product, then choice
+        GemmRtArgs g{k.x, W, 0, w.router, W, 1, 0, k.moe_z, k.ldz, 0, nullptr, T, R, W, 1, f32};
+        SPAN(5, 2.0 * T * R * W, gemm_rt(stream_, g));
+        SPAN(3, 8.0 * T * R, moe_route(stream_, k.moe_z, k.ldz, w.correction, f32, R, l.top_k, k.moe_ids, k.moe_w, T));
+      }
       const int items = T * l.top_k;
       if (moe_grouped_ok(model_, l) && k.moe_a16 && items >= 2 * E) {
         // items sorted by expert into 128-row segments; both products of every expert in two grouped tcgen05 launches
         const int rows = moe_group_max_rows(items, E);
         SPAN(3, 12.0 * items, moe_group_rows(stream_, k.moe_ids, items, l.top_k, E, k.moe_row_of, k.moe_src, k.moe_tiles));
         SPAN(3, 4.0 * rows * W, moe_gather_rows(stream_, x16, W, k.moe_src, k.moe_a16, rows));
-        GemmArgs g1{k.moe_a16, W, (const bf16*)w.w_gu, W, k.moe_gu, 2 * F, nullptr, 0, nullptr, rows, 2 * F, W, EPI_F32, 0};
+        GemmArgs g1{k.moe_a16, W, (const bf16*)w.w_gu, W, k.gu16, 2 * F, nullptr, 0, nullptr, rows, 2 * F, W, EPI_NONE, 0};
         g1.m_tile_group = k.moe_tiles; g1.groups = E;
         SPAN(0, 4.0 * rows * F * W, gemm_bf16_tn(stream_, g1));
-        SPAN(3, 10.0 * rows * F, gated_unit(stream_, k.moe_gu, 2 * F, GLU_SILU, nullptr, k.moe_h16, rows, F));
+        SPAN(3, 6.0 * rows * F, gated_unit_b16(stream_, k.gu16, 2 * F, GLU_SILU, k.moe_h16, rows, F));
         GemmArgs g2{k.moe_h16, F, (const bf16*)w.w_down, F, k.moe_y, W, nullptr, 0, nullptr, rows, W, F, EPI_F32, 0};
         g2.m_tile_group = k.moe_tiles; g2.groups = E;
         SPAN(0, 2.0 * rows * F * W, gemm_bf16_tn(stream_, g2));
@@ -670,9 +691,16 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       SPAN(3, 3 * rowb, resid(nullptr, w.norm2));
     } else if (l.ff > 0 && l.ff_kind == HB_FF_GELU_TANH) {
       const int F = l.ff;
-      rc = stack_gemm(k.x, x16, W, w.w_gu, 2 * F, W, k.p1, k.ld1, T);
-      if (rc != HB_OK) return rc;
-      SPAN(3, 12.0 * T * F, gated_unit(stream_, k.p1, k.ld1, GLU_GELU_TANH, k.mo, mo16, T, F));
+      if (T > 256 && k.gu16 && F % 8 == 0 && stack_tc(2 * F, W, W, W) && stack_tc(W, F, F, W)) {
+        // steps of many tokens: both products on the tcgen05 GEMM, the [gate | up] rows travel between them as bf16
+        GemmArgs g{x16, W, (const bf16*)w.w_gu, W, k.gu16, 2 * F, nullptr, 0, nullptr, T, 2 * F, W, EPI_NONE, 0};
+        SPAN(0, 4.0 * T * F * W, gemm_bf16_tn(stream_, g));
+        SPAN(3, 6.0 * T * F, gated_unit_b16(stream_, k.gu16, 2 * F, GLU_GELU_TANH, mo16, T, F));
+      } else {
+        rc = stack_gemm(k.x, x16, W, w.w_gu, 2 * F, W, k.p1, k.ld1, T);
+        if (rc != HB_OK) return rc;
+        SPAN(3, 12.0 * T * F, gated_unit(stream_, k.p1, k.ld1, GLU_GELU_TANH, k.mo, mo16, T, F));
+      }
       rc = stack_gemm(k.mo, mo16, F, w.w_down, W, F, k.y, W, T);
       if (rc != HB_OK) return rc;
       SPAN(3, 3 * rowb, resid(nullptr, w.norm2));

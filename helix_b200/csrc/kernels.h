@@ -125,6 +125,7 @@ struct AttnPrefillArgs {
   // counted from position 0 of the sequence).  unit_sink: one unit added to the softmax denominator (a key of score 0 that
   // carries no value)
   int block_mask = 0, unit_sink = 0;
+  const float* head_gate = nullptr; int ldg = 0;  // optional [T][>= Hq] fp32: head h of token t leaves times sigmoid(head_gate[t][h])
 };
 cudaError_t attn_prefill(cudaStream_t stream, const AttnPrefillArgs& a);
 // test-only CUDA-core checker, fp32 output [T, ldo]
@@ -399,6 +400,13 @@ cudaError_t gated_unit(cudaStream_t s, const float* gu, long ldg, int act, float
 // equals; ids[t, k] = chosen output, wts[t, k] = its score (not renormalised)
 cudaError_t moe_route(cudaStream_t s, const float* z, long ldz, const void* correction, bool f32, int R, int top_k, int32_t* ids,
                       float* wts, int T);
+// moe_route fused with the router's product: z = router x[t] in fp32 (router [R][W] of the weight type, held in shared
+// memory: moe_router_smem(R, W, f32) <= 200 KB, else use gemm_rt + moe_route), then the same choice.  sms: blocks to launch
+size_t moe_router_smem(int R, int W, bool f32);
+cudaError_t moe_router(cudaStream_t s, const float* x, const void* router, const void* correction, bool f32, int R, int W, int top_k,
+                       int32_t* ids, float* wts, int T, int sms);
+// bf16 form of gated_unit for the tensor-core path: gu and out are bf16, F and ldg multiples of eight
+cudaError_t gated_unit_b16(cudaStream_t s, const bf16* gu, long ldg, int act, bf16* out, int T, int F);
 // One block per (token, choice): y[(t, k), :] = down_e(silu(gate_e x_t) * (up_e x_t)) for ids[t, k] = e < E (rows of choices
 // that name an identity output are left alone).  x_b16 != null: the unit reads the bf16 copy of x and rounds its inner
 // activation to bf16, as the tensor-core path does.  w_gu: [E][2F][W] ([gate | up] rows), w_down: [E][W][F].

@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(kPrepThreads) gqa_prep_kernel(GqaPrepArgs a) {
 //   softmax:      fp32, the optional unit of the denominator enters as a key of score 0 without a value
 //   weighted sum: thread (slice, column) adds the keys of its slice for all HG heads; slices are added in slice order
 // dynamic smem (floats): q [HG][Dp] | scores [max_keys][HG] | partials [threads][HG] | red [32 * HG] | row index [max_keys]
-constexpr int kAttThreads = 256;
+constexpr int kAttThreads = 512;
 constexpr int kHG = 4;
 
 template <typename CT>
@@ -120,7 +120,38 @@ __global__ void __launch_bounds__(kAttThreads) gqa_attn_kernel(GqaAttnArgs a, in
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
   const CT* kc = (const CT*)a.k_cache;
   const CT* vc = (const CT*)a.v_cache;
-  if (sizeof(CT) == 2 && (D & 7) == 0) {
+  const int lpk = D / 8;  // lanes that cover one bf16 key row with one 16-byte load each
+  if (sizeof(CT) == 2 && (D & 7) == 0 && (lpk == 4 || lpk == 8 || lpk == 16 || lpk == 32)) {
+    // several keys per warp iteration: sub-warp `sub` of lpk lanes takes key base + sub; partial dot products are added
+    // inside the sub-warp by a butterfly, so a key's sum does not depend on which sub-warp took it
+    const int kpw = 32 / lpk, sub = l / lpk, li = l % lpk;
+    for (int base = w * kpw; base < n; base += nw * kpw) {
+      const int jj = base + sub;
+      const bool live = jj < n;
+      const bf16* row = reinterpret_cast<const bf16*>(kc) + (size_t)rowoff[live ? jj : n - 1] * D;
+      const uint4 u = *reinterpret_cast<const uint4*>(row + li * 8);
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+      float s[HG] = {};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(p2[e]);
+#pragma unroll
+        for (int hh = 0; hh < HG; ++hh) {
+          const float2 q = *reinterpret_cast<const float2*>(qs + hh * Dp + li * 8 + 2 * e);
+          s[hh] = fmaf(q.x, f.x, s[hh]);
+          s[hh] = fmaf(q.y, f.y, s[hh]);
+        }
+      }
+      for (int o = lpk >> 1; o > 0; o >>= 1) {
+#pragma unroll
+        for (int hh = 0; hh < HG; ++hh) s[hh] += __shfl_xor_sync(0xffffffffu, s[hh], o);
+      }
+      if (live && li == 0) {
+#pragma unroll
+        for (int hh = 0; hh < HG; ++hh) sc[jj * HG + hh] = s[hh] * a.scale;
+      }
+    }
+  } else if (sizeof(CT) == 2 && (D & 7) == 0) {
     // bf16 rows that start on 16-byte boundaries: a lane takes 8 consecutive entries per load
     for (int jj = w; jj < n; jj += nw) {
       const bf16* row = reinterpret_cast<const bf16*>(kc) + (size_t)rowoff[jj] * D;
@@ -201,6 +232,53 @@ __global__ void __launch_bounds__(kAttThreads) gqa_attn_kernel(GqaAttnArgs a, in
     float gate = 1.f;
     if (a.gate && hh < nh) gate = sigmoidf_(a.gate[(size_t)t * a.ldg + h0 + hh]);
     inv[hh] = gate / tot;
+  }
+  const int ncg = Dv / 16;  // groups of 16 value columns (one 32-byte piece of a bf16 row)
+  if (sizeof(CT) == 2 && (Dv & 15) == 0 && ncg <= nw) {
+    // warp (column group cg, half): its 32 lanes take every (32 * halves)-th key and keep 16 columns x HG heads in registers;
+    // lanes are added by a butterfly, halves in order through shared memory
+    const int halves = nw / ncg, cg = w % ncg, half = w / ncg, NSv = halves * 32;
+    float acc[HG][16] = {};
+    if (half < halves) {
+      for (int jj = half * 32 + l; jj < n; jj += NSv) {
+        const uint4* vrow = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(vc) + (size_t)rowoff[jj] * Dv + cg * 16);
+        const uint4 u0 = vrow[0], u1 = vrow[1];
+        const float4 p = *reinterpret_cast<const float4*>(sc + jj * HG);
+        const float pw[HG] = {p.x, p.y, p.z, p.w};
+        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&u0);
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&u1);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 fa = __bfloat1622float2(a2[e]), fb = __bfloat1622float2(b2[e]);
+#pragma unroll
+          for (int hh = 0; hh < HG; ++hh) {
+            acc[hh][2 * e] = fmaf(pw[hh], fa.x, acc[hh][2 * e]);
+            acc[hh][2 * e + 1] = fmaf(pw[hh], fa.y, acc[hh][2 * e + 1]);
+            acc[hh][8 + 2 * e] = fmaf(pw[hh], fb.x, acc[hh][8 + 2 * e]);
+            acc[hh][8 + 2 * e + 1] = fmaf(pw[hh], fb.y, acc[hh][8 + 2 * e + 1]);
+          }
+        }
+      }
+#pragma unroll
+      for (int hh = 0; hh < HG; ++hh)
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float v = warp_sum(acc[hh][e]);
+          if (l == e) part[((size_t)half * Dv + cg * 16 + e) * HG + hh] = v;
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < Dv * HG; e += blockDim.x) {
+      const int r = e / HG, hh = e % HG;
+      if (hh >= nh) continue;
+      float tot = 0.f;
+      for (int hf = 0; hf < halves; ++hf) tot += part[((size_t)hf * Dv + r) * HG + hh];
+      const size_t o = (size_t)t * a.ldo + (size_t)(h0 + hh) * Dv + r;
+      const float v = tot * inv[hh];
+      a.out[o] = v;
+      if (a.out_b16) a.out_b16[o] = __float2bfloat16(v);
+    }
+    return;
   }
   const int Rp = (Dv + 31) / 32 * 32;
   const int NS = max(1, (int)blockDim.x / Rp);  // key slices

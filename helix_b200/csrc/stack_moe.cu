@@ -3,6 +3,8 @@
 // choice), weighted combination with identity outputs.  Every sum has a fixed order per output element.
 #include <math.h>
 
+#include <algorithm>
+
 #include "kernels.h"
 #include "launch.h"
 #include "stack_common.cuh"
@@ -40,16 +42,10 @@ __global__ void gated_unit_kernel(const float* __restrict__ gu, long ldg, int ac
   }
 }
 
-// One warp per token.  dynamic smem: per warp R floats (the choice scores while the top-k is taken)
+// The choice of one token by one warp: zr[R] router logits (global or shared memory), pick[R] scratch in shared memory.
 template <typename WT>
-__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ z, long ldz, const WT* __restrict__ corr, int R,
-                                                        int top_k, int32_t* __restrict__ ids, float* __restrict__ wts, int T) {
-  extern __shared__ float sm[];
-  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + w;
-  if (t >= T) return;
-  float* pick = sm + (size_t)w * R;
-  const float* zr = z + (size_t)t * ldz;
+__device__ __forceinline__ void route_one(const float* zr, const WT* __restrict__ corr, int R, int top_k, float* pick,
+                                          int32_t* __restrict__ ids, float* __restrict__ wts, int l) {
   float mx = -INFINITY;
   for (int i = l; i < R; i += 32) mx = fmaxf(mx, zr[i]);
   mx = warp_max(mx);
@@ -73,12 +69,79 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
       if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
     }
     if (l == 0) {
-      ids[(size_t)t * top_k + k] = bi;
-      wts[(size_t)t * top_k + k] = expf(zr[bi] - mx) * inv;  // the score itself, without the correction
+      ids[k] = bi;
+      wts[k] = expf(zr[bi] - mx) * inv;  // the score itself, without the correction
       pick[bi] = -INFINITY;
     }
     __syncwarp();
   }
+}
+
+// One warp per token.  dynamic smem: per warp R floats (the choice scores while the top-k is taken)
+template <typename WT>
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ z, long ldz, const WT* __restrict__ corr, int R,
+                                                        int top_k, int32_t* __restrict__ ids, float* __restrict__ wts, int T) {
+  extern __shared__ float sm[];
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + w;
+  if (t >= T) return;
+  route_one<WT>(z + (size_t)t * ldz, corr, R, top_k, sm + (size_t)w * R, ids + (size_t)t * top_k, wts + (size_t)t * top_k, l);
+}
+
+// Router logits and choice in one kernel: the router's rows stay in shared memory, every warp takes tokens in turn and
+// forms the R dot products of its token's fp32 row (lanes stride the row, eight outputs per pass), then chooses.
+// dynamic smem: router [R][W] of WT | per warp: logits [R] + scratch [R]
+constexpr int kRouterWarps = 8;
+template <typename WT>
+__global__ void __launch_bounds__(kRouterWarps * 32) moe_router_kernel(const float* __restrict__ x, const WT* __restrict__ router,
+                                                                       const WT* __restrict__ corr, int R, int W, int top_k,
+                                                                       int32_t* __restrict__ ids, float* __restrict__ wts, int T) {
+  extern __shared__ float sm[];
+  WT* rw = reinterpret_cast<WT*>(sm);
+  float* zs = sm + ((size_t)R * W * sizeof(WT) + 15) / 16 * 4;
+  for (size_t i = threadIdx.x; i < (size_t)R * W; i += blockDim.x) rw[i] = router[i];
+  __syncthreads();
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  float* z = zs + (size_t)w * 2 * R;
+  for (int t = blockIdx.x * kRouterWarps + w; t < T; t += gridDim.x * kRouterWarps) {
+    const float* xr = x + (size_t)t * W;
+    for (int r0 = 0; r0 < R; r0 += 8) {
+      float acc[8] = {};
+      for (int i = l; i < W; i += 32) {
+        const float xv = xr[i];
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          if (r0 + c < R) acc[c] = fmaf(xv, ldf<WT>(rw, (size_t)(r0 + c) * W + i), acc[c]);
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float v = warp_sum(acc[c]);
+        if (l == 0 && r0 + c < R) z[r0 + c] = v;
+      }
+    }
+    __syncwarp();
+    route_one<WT>(z, corr, R, top_k, z + R, ids + (size_t)t * top_k, wts + (size_t)t * top_k, l);
+    __syncwarp();
+  }
+}
+
+// bf16 in, bf16 out: h[t, j] = act(gu[t, j]) * gu[t, F + j], eight columns per thread (F and ldg multiples of eight)
+__global__ void gated_unit_b16_kernel(const bf16* __restrict__ gu, long ldg, int act, bf16* __restrict__ out, int F) {
+  const size_t t = blockIdx.x;
+  const int j = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (j >= F) return;
+  const uint4 g4 = *reinterpret_cast<const uint4*>(gu + t * ldg + j);
+  const uint4 u4 = *reinterpret_cast<const uint4*>(gu + t * ldg + F + j);
+  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+  const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+  uint4 o4;
+  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
+    o2[e] = __floats2bfloat162_rn(glu_act(g.x, act) * u.x, glu_act(g.y, act) * u.y);
+  }
+  *reinterpret_cast<uint4*>(out + t * F + j) = o4;
 }
 
 // dot product of a weight row with a vector in shared memory, lanes striding the row; every lane gets the sum
@@ -247,6 +310,8 @@ cudaError_t moe_combine_rows(cudaStream_t s, const float* x, const float* y, con
 cudaError_t stack_moe_init() {
   cudaError_t e;
   const int big = 200 * 1024;
+  if ((e = cudaFuncSetAttribute(moe_router_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(moe_router_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big)) != cudaSuccess) return e;
   if ((e = cudaFuncSetAttribute(moe_expert_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big)) != cudaSuccess) return e;
   if ((e = cudaFuncSetAttribute(moe_expert_rows_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big)) != cudaSuccess) return e;
   return cudaSuccess;
@@ -268,6 +333,27 @@ cudaError_t moe_route(cudaStream_t s, const float* z, long ldz, const void* corr
   const size_t smem = (size_t)4 * R * 4;
   if (f32) moe_route_kernel<float><<<(T + 3) / 4, 128, smem, s>>>(z, ldz, (const float*)corr, R, top_k, ids, wts, T);
   else moe_route_kernel<bf16><<<(T + 3) / 4, 128, smem, s>>>(z, ldz, (const bf16*)corr, R, top_k, ids, wts, T);
+  return cudaGetLastError();
+}
+
+size_t moe_router_smem(int R, int W, bool f32) {
+  return ((size_t)R * W * (f32 ? 4 : 2) + 15) / 16 * 16 + (size_t)kRouterWarps * 2 * R * 4;
+}
+cudaError_t moe_router(cudaStream_t s, const float* x, const void* router, const void* corr, bool f32, int R, int W, int top_k,
+                       int32_t* ids, float* wts, int T, int sms) {
+  if (T <= 0) return cudaSuccess;
+  const size_t smem = moe_router_smem(R, W, f32);
+  if (R <= 0 || top_k <= 0 || top_k > R || smem > 200 * 1024) return cudaErrorInvalidValue;
+  const int grid = std::max(1, std::min((T + kRouterWarps - 1) / kRouterWarps, sms > 0 ? sms : 148));
+  if (f32) moe_router_kernel<float><<<grid, kRouterWarps * 32, smem, s>>>(x, (const float*)router, (const float*)corr, R, W, top_k, ids, wts, T);
+  else moe_router_kernel<bf16><<<grid, kRouterWarps * 32, smem, s>>>(x, (const bf16*)router, (const bf16*)corr, R, W, top_k, ids, wts, T);
+  return cudaGetLastError();
+}
+
+cudaError_t gated_unit_b16(cudaStream_t s, const bf16* gu, long ldg, int act, bf16* out, int T, int F) {
+  if (T <= 0) return cudaSuccess;
+  if (F % 8 || ldg % 8 || ((uintptr_t)gu & 15) || ((uintptr_t)out & 15)) return cudaErrorInvalidValue;
+  gated_unit_b16_kernel<<<dim3(T, (F / 8 + 255) / 256), 256, 0, s>>>(gu, ldg, act, out, F);
   return cudaGetLastError();
 }
 
