@@ -112,8 +112,11 @@ int Engine::load_random_stack(const hb_stack_desc& sd, const hb_layer_desc* laye
     const float amp = p.is_norm_gain ? 0.f : (p.is_bias ? 0.1f : sqrtf(3.0f / (float)p.cols));
     const float mean = p.is_norm_gain ? p.fill : 0.f;
     const uint64_t sk = seed * 0x9E3779B97F4A7C15ull + (++k) * 0xD1B54A32D192ED03ull + std::hash<std::string>{}(kv.first);
+    // [128 gate | 128 up] tiles: the gate and up placements share a base; random values need no interleaving, the up
+    // tensor's share of the block is simply its second half
+    bf16* dst = p.dst + (p.mode == 2 ? n : 0);
     if (p.elem == 4) fill_uniform_kernel<float><<<148 * 4, 256, 0, stream_>>>((float*)p.dst, n, sk, amp, mean);
-    else fill_uniform_kernel<bf16><<<148 * 4, 256, 0, stream_>>>(p.dst, n, sk, amp, mean);
+    else fill_uniform_kernel<bf16><<<148 * 4, 256, 0, stream_>>>(dst, n, sk, amp, mean);
     CU(cudaGetLastError());
     model_.filled[kv.first] = true;
   }
@@ -526,7 +529,7 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       int longest = 0;
       for (const StepEntry& en : step_entries_) longest = std::max(longest, en.n);
       fused = fused && longest >= kAttDenseMin;
-      pa.q = k.p2; pa.ldq = H * Dk; pa.q_b16 = fused ? k.q16 : nullptr;
+      pa.q = fused ? nullptr : k.p2; pa.ldq = H * Dk; pa.q_b16 = fused ? k.q16 : nullptr;
       pa.k_cache = kplane; pa.v_cache = vplane; pa.f32 = f32;
       pa.slots = slots; pa.positions = positions;
       pa.freqs = k.freqs[i]; pa.rope_dims = l.rope_dims; pa.pairing = l.rope_pairing;
@@ -676,16 +679,22 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
         const int rows = moe_group_max_rows(items, E);
         SPAN(3, 12.0 * items, moe_group_rows(stream_, k.moe_ids, items, l.top_k, E, k.moe_row_of, k.moe_src, k.moe_tiles));
         SPAN(3, 4.0 * rows * W, moe_gather_rows(stream_, x16, W, k.moe_src, k.moe_a16, rows));
-        GemmArgs g1{k.moe_a16, W, (const bf16*)w.w_gu, W, k.gu16, 2 * F, nullptr, 0, nullptr, rows, 2 * F, W, EPI_NONE, 0};
-        g1.m_tile_group = k.moe_tiles; g1.groups = E;
-        SPAN(0, 4.0 * rows * F * W, gemm_bf16_tn(stream_, g1));
-        SPAN(3, 6.0 * rows * F, gated_unit_b16(stream_, k.gu16, 2 * F, GLU_SILU, k.moe_h16, rows, F));
+        if (w.gu_packed) {  // silu(gate) * up on the accumulators' way out
+          GemmArgs g1{k.moe_a16, W, (const bf16*)w.w_gu, W, k.moe_h16, F, nullptr, 0, nullptr, rows, 2 * F, W, EPI_SWIGLU, 0};
+          g1.m_tile_group = k.moe_tiles; g1.groups = E;
+          SPAN(0, 4.0 * rows * F * W, gemm_bf16_tn(stream_, g1));
+        } else {
+          GemmArgs g1{k.moe_a16, W, (const bf16*)w.w_gu, W, k.gu16, 2 * F, nullptr, 0, nullptr, rows, 2 * F, W, EPI_NONE, 0};
+          g1.m_tile_group = k.moe_tiles; g1.groups = E;
+          SPAN(0, 4.0 * rows * F * W, gemm_bf16_tn(stream_, g1));
+          SPAN(3, 6.0 * rows * F, gated_unit_b16(stream_, k.gu16, 2 * F, GLU_SILU, k.moe_h16, rows, F));
+        }
         GemmArgs g2{k.moe_h16, F, (const bf16*)w.w_down, F, k.moe_y, W, nullptr, 0, nullptr, rows, W, F, EPI_F32, 0};
         g2.m_tile_group = k.moe_tiles; g2.groups = E;
         SPAN(0, 2.0 * rows * F * W, gemm_bf16_tn(stream_, g2));
         SPAN(3, 4.0 * T * (l.top_k + 2) * W, moe_combine_rows(stream_, k.x, k.moe_y, k.moe_row_of, k.moe_w, l.top_k, k.y, T, W));
       } else {
-        SPAN(5, 6.0 * items * F * W, moe_expert_rows(stream_, k.x, x16, w.w_gu, w.w_down, f32, k.moe_ids, l.top_k, E, F, W, k.moe_y, T));
+        SPAN(5, 6.0 * items * F * W, moe_expert_rows(stream_, k.x, x16, w.w_gu, w.w_down, f32, k.moe_ids, l.top_k, E, F, W, k.moe_y, T, w.gu_packed));
         SPAN(3, 4.0 * T * (l.top_k + 2) * W, moe_combine(stream_, k.x, k.moe_y, k.moe_ids, k.moe_w, l.top_k, E, k.y, T, W));
       }
       SPAN(3, 3 * rowb, resid(nullptr, w.norm2));
@@ -693,13 +702,18 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       const int F = l.ff;
       if (T > 256 && k.gu16 && F % 8 == 0 && stack_tc(2 * F, W, W, W) && stack_tc(W, F, F, W)) {
         // steps of many tokens: both products on the tcgen05 GEMM, the [gate | up] rows travel between them as bf16
-        GemmArgs g{x16, W, (const bf16*)w.w_gu, W, k.gu16, 2 * F, nullptr, 0, nullptr, T, 2 * F, W, EPI_NONE, 0};
-        SPAN(0, 4.0 * T * F * W, gemm_bf16_tn(stream_, g));
-        SPAN(3, 6.0 * T * F, gated_unit_b16(stream_, k.gu16, 2 * F, GLU_GELU_TANH, mo16, T, F));
+        if (w.gu_packed) {  // gelu_tanh(gate) * up on the accumulators' way out
+          GemmArgs g{x16, W, (const bf16*)w.w_gu, W, mo16, F, nullptr, 0, nullptr, T, 2 * F, W, EPI_GEGLU, 0};
+          SPAN(0, 4.0 * T * F * W, gemm_bf16_tn(stream_, g));
+        } else {
+          GemmArgs g{x16, W, (const bf16*)w.w_gu, W, k.gu16, 2 * F, nullptr, 0, nullptr, T, 2 * F, W, EPI_NONE, 0};
+          SPAN(0, 4.0 * T * F * W, gemm_bf16_tn(stream_, g));
+          SPAN(3, 6.0 * T * F, gated_unit_b16(stream_, k.gu16, 2 * F, GLU_GELU_TANH, mo16, T, F));
+        }
       } else {
         rc = stack_gemm(k.x, x16, W, w.w_gu, 2 * F, W, k.p1, k.ld1, T);
         if (rc != HB_OK) return rc;
-        SPAN(3, 12.0 * T * F, gated_unit(stream_, k.p1, k.ld1, GLU_GELU_TANH, k.mo, mo16, T, F));
+        SPAN(3, 12.0 * T * F, gated_unit(stream_, k.p1, k.ld1, GLU_GELU_TANH, k.mo, mo16, T, F, w.gu_packed));
       }
       rc = stack_gemm(k.mo, mo16, F, w.w_down, W, F, k.y, W, T);
       if (rc != HB_OK) return rc;

@@ -88,6 +88,9 @@ __device__ __forceinline__ void gelu_erf2(float& x0, float& x1) {
   const uint64_t hx = f2_mul(x, c2(0.5f));
   f2_unpack(f2_fma(hx, e, hx), x0, x1);
 }
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 
 template <int BN, int EPI, int CG = 1>
@@ -104,7 +107,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int tile_workers = (CG == 2) ? (gridDim.x >> 1) : gridDim.x;
   constexpr int STAGES = C::STAGES;
   constexpr bool kF32 = (EPI == EPI_F32);
-  constexpr bool kSwiGLU = (EPI == EPI_SWIGLU);
+  constexpr bool kSwiGLU = (EPI == EPI_SWIGLU || EPI == EPI_GEGLU);  // gated unit over [128 gate | 128 up] tiles
   constexpr bool kResid = (EPI == EPI_RESID || EPI == EPI_BIAS_RESID);
   constexpr bool kBias = (EPI == EPI_BIAS || EPI == EPI_BIAS_GELU || EPI == EPI_BIAS_RESID);
   constexpr bool kRope = (EPI == EPI_ROPE);
@@ -387,7 +390,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               tmem_ld_32x32b_x32(t_tile + 128 + col, u);
               tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 32; ++j) f[j] = silu(__uint_as_float(v[j])) * __uint_as_float(u[j]);
+              for (int j = 0; j < 32; ++j)
+                f[j] = (EPI == EPI_GEGLU ? gelu_tanh_f(__uint_as_float(v[j])) : silu(__uint_as_float(v[j]))) * __uint_as_float(u[j]);
             } else {
               tmem_ld_wait();
 #pragma unroll
@@ -470,7 +474,7 @@ template <int BN, int EPI, int CG>
 cudaError_t launch_cfg(cudaStream_t stream, const GemmArgs& g, int num_sms) {
   using C = Cfg<BN, CG>;
   constexpr bool kF32 = (EPI == EPI_F32);
-  constexpr bool kSwiGLU = (EPI == EPI_SWIGLU);
+  constexpr bool kSwiGLU = (EPI == EPI_SWIGLU || EPI == EPI_GEGLU);
   constexpr int TILE_M = BLOCK_M * CG;
   CUtensorMap ma, mb, mc, mr;
   const int n_out = kSwiGLU ? g.N / 2 : g.N;
@@ -545,10 +549,10 @@ cudaError_t launch_epi(cudaStream_t stream, const GemmArgs& g, int num_sms) {
       if (use_pair() && !g.m_tile_group && (long)((g.M + 255) / 256) * ((g.N + 255) / 256) >= num_sms / 2) return launch_cfg<256, EPI, 2>(stream, g, num_sms);
       return launch_cfg<256, EPI, 1>(stream, g, num_sms);
     case 128:
-      if constexpr (EPI != EPI_SWIGLU && EPI != EPI_ROPE) return launch_cfg<128, EPI, 1>(stream, g, num_sms);
+      if constexpr (EPI != EPI_SWIGLU && EPI != EPI_GEGLU && EPI != EPI_ROPE) return launch_cfg<128, EPI, 1>(stream, g, num_sms);
       return cudaErrorInvalidValue;
     case 64:
-      if constexpr (EPI != EPI_SWIGLU && EPI != EPI_ROPE) return launch_cfg<64, EPI, 1>(stream, g, num_sms);
+      if constexpr (EPI != EPI_SWIGLU && EPI != EPI_GEGLU && EPI != EPI_ROPE) return launch_cfg<64, EPI, 1>(stream, g, num_sms);
       return cudaErrorInvalidValue;
     default: return cudaErrorInvalidValue;
   }
@@ -566,7 +570,7 @@ cudaError_t set_attr_epi() {
   cudaError_t e;
   if ((e = set_attr<256, EPI, 2>()) != cudaSuccess) return e;
   if ((e = set_attr<256, EPI, 1>()) != cudaSuccess) return e;
-  if constexpr (EPI != EPI_SWIGLU && EPI != EPI_ROPE) {
+  if constexpr (EPI != EPI_SWIGLU && EPI != EPI_GEGLU && EPI != EPI_ROPE) {
     if ((e = set_attr<128, EPI, 1>()) != cudaSuccess) return e;
     return set_attr<64, EPI, 1>();
   }
@@ -583,6 +587,7 @@ cudaError_t gemm_init() {
   if ((e = set_attr_epi<EPI_BIAS_RESID>()) != cudaSuccess) return e;
   if ((e = set_attr_epi<EPI_F32>()) != cudaSuccess) return e;
   if ((e = set_attr_epi<EPI_ROPE>()) != cudaSuccess) return e;
+  if ((e = set_attr_epi<EPI_GEGLU>()) != cudaSuccess) return e;
   return set_attr_epi<EPI_SWIGLU>();
 }
 
@@ -615,6 +620,12 @@ cudaError_t gemm_bf16_tn(cudaStream_t stream, const GemmArgs& g) {
       GemmArgs h = g;
       h.block_n = 256;
       return launch_epi<EPI_SWIGLU>(stream, h, sms);
+    }
+    case EPI_GEGLU: {
+      if (g.N % 256) return cudaErrorInvalidValue;
+      GemmArgs h = g;
+      h.block_n = 256;
+      return launch_epi<EPI_GEGLU>(stream, h, sms);
     }
     case EPI_F32: return launch_epi<EPI_F32>(stream, g, sms);
     case EPI_ROPE: {

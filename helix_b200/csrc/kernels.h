@@ -26,6 +26,7 @@ enum Epi : int {
   EPI_SWIGLU = 5,      // W rows packed per 256-row tile as [128 gate | 128 up];
                        // C[m, tile*128+j] = silu(gate_j) * up_j   (bf16, ldc counts N/2 columns)
   EPI_F32 = 6,         // C = acc                              (fp32)
+  EPI_GEGLU = 8,       // as EPI_SWIGLU with gelu_tanh(gate_j) * up_j
   EPI_ROPE = 7,        // fused QKV projection of a decoder: C = bf16(acc [+ bias]) with the q and k heads rotated
                        // (RopeEpi) and the k / v rows also scattered into the paged KV cache
 };
@@ -358,7 +359,8 @@ cudaError_t stack_gqa_init();
 enum StackMask : int { MASK_WINDOW = 0, MASK_CHUNK = 1, MASK_CAUSAL = 2 };  // == hb_mask
 // From the fused projection p[t] = [q (H*D) | k (G*D) | v (G*Dv, or the k columns again) | ...]: the first rope_dims entries of
 // every q and k head turn by pos * freqs[i] (pairing 1: entries (2i, 2i+1); 0: (i, i + rope_dims/2); angles in double
-// precision), then q and k are divided by their root mean square over D when unit_norm.  q goes to q[t, h*D..] (+ bf16 copy),
+// precision), then q and k are divided by their root mean square over D when unit_norm.  q goes to q[t, h*D..] and / or its
+// bf16 copy (either may be null),
 // k and the UNTOUCHED v columns to the cache rows of slots[t] (slot < 0: no cache write).
 struct GqaPrepArgs {
   const float* p; long ldp; int q_off, k_off, v_off;
@@ -395,7 +397,9 @@ cudaError_t head_gate_rows(cudaStream_t s, const bf16* o, long ldo, const float*
 cudaError_t stack_moe_init();
 enum GluAct : int { GLU_SILU = 0, GLU_GELU_TANH = 1 };
 // out[t, j] = act(gu[t, j]) * gu[t, F + j]   (row stride ldg; out may be null when only the bf16 copy is wanted)
-cudaError_t gated_unit(cudaStream_t s, const float* gu, long ldg, int act, float* out, bf16* out_b16, int T, int F);
+// packed: the columns come from weights stored per 256-row tile as [128 gate | 128 up] (the layout of EPI_SWIGLU / EPI_GEGLU):
+// gate j of tile i at column 256 i + j, its up at 256 i + 128 + j, output column 128 i + j (F a multiple of 128)
+cudaError_t gated_unit(cudaStream_t s, const float* gu, long ldg, int act, float* out, bf16* out_b16, int T, int F, bool packed = false);
 // Router: scores = softmax(z[t, :R]) in fp32; the top_k largest of (score + correction) are chosen, lowest index first among
 // equals; ids[t, k] = chosen output, wts[t, k] = its score (not renormalised)
 cudaError_t moe_route(cudaStream_t s, const float* z, long ldz, const void* correction, bool f32, int R, int top_k, int32_t* ids,
@@ -411,7 +415,7 @@ cudaError_t gated_unit_b16(cudaStream_t s, const bf16* gu, long ldg, int act, bf
 // that name an identity output are left alone).  x_b16 != null: the unit reads the bf16 copy of x and rounds its inner
 // activation to bf16, as the tensor-core path does.  w_gu: [E][2F][W] ([gate | up] rows), w_down: [E][W][F].
 cudaError_t moe_expert_rows(cudaStream_t s, const float* x, const bf16* x_b16, const void* w_gu, const void* w_down, bool f32,
-                            const int32_t* ids, int top_k, int E, int F, int W, float* y, int T);
+                            const int32_t* ids, int top_k, int E, int F, int W, float* y, int T, bool packed = false);
 // The same experts as grouped tensor-core products (bf16 mode): moe_group_rows sorts the (token, choice) items by expert into
 // a row buffer of moe_group_max_rows(items, E) rows whose per-expert segments start on multiples of 128 rows (row_of[item] =
 // its row or -1 for an identity output, src_of_row[row] = its token or -1, tile_group[row / 128] = the expert whose weights

@@ -241,9 +241,10 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
     return p;
   };
   auto put = [&](const std::string& name, uint8_t* dst, size_t row_off, size_t rows, size_t cols, bool gain = false, float fill = 1.f,
-                 bool bias = false) {
+                 bool bias = false, int mode = 0) {
     if (!m) return;
     Placement p;
+    p.mode = mode;
     p.dst = reinterpret_cast<bf16*>(dst ? dst + row_off * cols * es : nullptr);
     p.rows = rows;
     p.cols = cols;
@@ -375,22 +376,26 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
       put(p + "norm2", n2, 0, W, 1, true, gain_fill);
       put(p + "mlp.router", router, 0, R, W);
       put(p + "mlp.correction", corr, 0, R, 1, false, 1.f, true);
+      const bool packed = !d.compute_f32 && Fn % 128 == 0;
       for (size_t e = 0; e < E; ++e) {
         const std::string pe = p + "mlp.e" + std::to_string(e) + ".";
-        put(pe + "gate", gu, e * 2 * Fn, Fn, W);
-        put(pe + "up", gu, e * 2 * Fn + Fn, Fn, W);
+        put(pe + "gate", gu, e * 2 * Fn, Fn, W, false, 1.f, false, packed ? 1 : 0);
+        put(pe + "up", gu, e * 2 * Fn + (packed ? 0 : Fn), Fn, W, false, 1.f, false, packed ? 2 : 0);
         put(pe + "down", dn, e * W, W, Fn);
       }
+      w.gu_packed = packed;
       w.norm2 = n2; w.router = router; w.correction = corr; w.w_gu = gu; w.w_down = dn;
     } else if (l.ff > 0 && l.ff_kind == HB_FF_GELU_TANH) {
       const size_t Fn = l.ff;
       uint8_t* n2 = take(W);
       uint8_t* gu = take(2 * Fn * W);
       uint8_t* dn = take(W * Fn);
+      const bool packed = !d.compute_f32 && Fn % 128 == 0;
       put(p + "norm2", n2, 0, W, 1, true, gain_fill);
-      put(p + "mlp.gate", gu, 0, Fn, W);
-      put(p + "mlp.up", gu, Fn, Fn, W);
+      put(p + "mlp.gate", gu, 0, Fn, W, false, 1.f, false, packed ? 1 : 0);
+      put(p + "mlp.up", gu, packed ? 0 : Fn, Fn, W, false, 1.f, false, packed ? 2 : 0);
       put(p + "mlp.down", dn, 0, W, Fn);
+      w.gu_packed = packed;
       w.norm2 = n2; w.w_gu = gu; w.w_down = dn;
     } else if (l.ff > 0) {
       const size_t Fn = l.ff;

@@ -41,6 +41,9 @@ struct StackLayerW {
   // mixture of experts: router rows and choice corrections for experts + identity outputs; expert e's [gate | up] rows at
   // w_gu + e * 2 ff * width, its down-projection at w_down + e * width * ff
   void *router = nullptr, *correction = nullptr;
+  // bf16 mode, ff a multiple of 128 (tanh-GELU unit, experts): [gate | up] rows stored per 256-row tile as [128 gate | 128 up],
+  // the layout the gated epilogue of the tcgen05 GEMM reads; every other consumer indexes through it
+  bool gu_packed = false;
 };
 
 // where an uploaded checkpoint tensor lands inside the arena

@@ -58,11 +58,11 @@ __global__ void __launch_bounds__(kPrepThreads) gqa_prep_kernel(GqaPrepArgs a) {
       rs = 1.f / sqrtf(ss / (float)a.D + a.eps);
     }
     if (isq) {
-      float* dst = a.q + (size_t)t * a.ldq + (size_t)head * a.D;
+      float* dst = a.q ? a.q + (size_t)t * a.ldq + (size_t)head * a.D : nullptr;
       bf16* dstb = a.q_b16 ? a.q_b16 + (size_t)t * a.ldq + (size_t)head * a.D : nullptr;
       for (int i = lane; i < a.D; i += 32) {
         const float v = buf[i] * rs;
-        dst[i] = v;
+        if (dst) dst[i] = v;
         if (dstb) dstb[i] = __float2bfloat16(v);
       }
     } else if (slot >= 0) {

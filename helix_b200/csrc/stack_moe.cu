@@ -17,28 +17,30 @@ __device__ __forceinline__ float gelu_tanh_(float z) {
 }
 __device__ __forceinline__ float glu_act(float z, int act) { return act == GLU_GELU_TANH ? gelu_tanh_(z) : z * sigmoidf_(z); }
 
-// VEC = 4: F and ldg are multiples of four (16-byte loads and stores)
-template <int VEC>
+// VEC = 4: F and ldg are multiples of four (16-byte loads and stores).  PACKED: gate j of tile i sits at column 256 i + j and
+// its up at 256 i + 128 + j (weights stored per 256-row tile as [128 gate | 128 up]); the output column is 128 i + j
+template <int VEC, bool PACKED>
 __global__ void gated_unit_kernel(const float* __restrict__ gu, long ldg, int act, float* __restrict__ out, bf16* __restrict__ outb, int F) {
   const size_t t = blockIdx.x;
   const int j = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
   if (j >= F) return;
+  const size_t gi = PACKED ? (size_t)(j >> 7) * 256 + (j & 127) : (size_t)j, ui = PACKED ? gi + 128 : (size_t)F + j;
   if (VEC == 4) {
-    const float4 g = *reinterpret_cast<const float4*>(gu + (size_t)t * ldg + j);
-    const float4 u = *reinterpret_cast<const float4*>(gu + (size_t)t * ldg + F + j);
+    const float4 g = *reinterpret_cast<const float4*>(gu + t * ldg + gi);
+    const float4 u = *reinterpret_cast<const float4*>(gu + t * ldg + ui);
     const float v0 = glu_act(g.x, act) * u.x, v1 = glu_act(g.y, act) * u.y, v2 = glu_act(g.z, act) * u.z, v3 = glu_act(g.w, act) * u.w;
-    if (out) *reinterpret_cast<float4*>(out + (size_t)t * F + j) = make_float4(v0, v1, v2, v3);
+    if (out) *reinterpret_cast<float4*>(out + t * F + j) = make_float4(v0, v1, v2, v3);
     if (outb) {
       __nv_bfloat162 lo = __floats2bfloat162_rn(v0, v1), hi = __floats2bfloat162_rn(v2, v3);
       uint2 pk;
       pk.x = *reinterpret_cast<unsigned*>(&lo);
       pk.y = *reinterpret_cast<unsigned*>(&hi);
-      *reinterpret_cast<uint2*>(outb + (size_t)t * F + j) = pk;
+      *reinterpret_cast<uint2*>(outb + t * F + j) = pk;
     }
   } else {
-    const float v = glu_act(gu[(size_t)t * ldg + j], act) * gu[(size_t)t * ldg + F + j];
-    if (out) out[(size_t)t * F + j] = v;
-    if (outb) outb[(size_t)t * F + j] = __float2bfloat16(v);
+    const float v = glu_act(gu[t * ldg + gi], act) * gu[t * ldg + ui];
+    if (out) out[t * F + j] = v;
+    if (outb) outb[t * F + j] = __float2bfloat16(v);
   }
 }
 
@@ -89,9 +91,18 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 }
 
 // Router logits and choice in one kernel: the router's rows stay in shared memory, every warp takes tokens in turn and
-// forms the R dot products of its token's fp32 row (lanes stride the row, eight outputs per pass), then chooses.
+// forms the R dot products of its token's fp32 row (lanes stride the row four entries at a time, kRouterRT outputs per pass
+// so that a pass keeps many independent loads in flight), then chooses.
 // dynamic smem: router [R][W] of WT | per warp: logits [R] + scratch [R]
-constexpr int kRouterWarps = 8;
+constexpr int kRouterWarps = 16;
+constexpr int kRouterRT = 16;
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const bf16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
 template <typename WT>
 __global__ void __launch_bounds__(kRouterWarps * 32) moe_router_kernel(const float* __restrict__ x, const WT* __restrict__ router,
                                                                        const WT* __restrict__ corr, int R, int W, int top_k,
@@ -99,22 +110,42 @@ __global__ void __launch_bounds__(kRouterWarps * 32) moe_router_kernel(const flo
   extern __shared__ float sm[];
   WT* rw = reinterpret_cast<WT*>(sm);
   float* zs = sm + ((size_t)R * W * sizeof(WT) + 15) / 16 * 4;
-  for (size_t i = threadIdx.x; i < (size_t)R * W; i += blockDim.x) rw[i] = router[i];
+  {
+    const size_t bytes = (size_t)R * W * sizeof(WT), n16 = ((uintptr_t)router & 15) ? 0 : bytes / 16;
+    const uint4* src = reinterpret_cast<const uint4*>(router);
+    uint4* dst = reinterpret_cast<uint4*>(sm);
+    for (size_t i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
+    for (size_t i = n16 * 16 / sizeof(WT) + threadIdx.x; i < (size_t)R * W; i += blockDim.x) rw[i] = router[i];
+  }
   __syncthreads();
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
   float* z = zs + (size_t)w * 2 * R;
   for (int t = blockIdx.x * kRouterWarps + w; t < T; t += gridDim.x * kRouterWarps) {
     const float* xr = x + (size_t)t * W;
-    for (int r0 = 0; r0 < R; r0 += 8) {
-      float acc[8] = {};
-      for (int i = l; i < W; i += 32) {
-        const float xv = xr[i];
+    for (int r0 = 0; r0 < R; r0 += kRouterRT) {
+      float acc[kRouterRT] = {};
+      if ((W & 3) == 0) {
+#pragma unroll 2
+        for (int i = l * 4; i < W; i += 128) {
+          const float4 xv = ld4(xr + i);
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-          if (r0 + c < R) acc[c] = fmaf(xv, ldf<WT>(rw, (size_t)(r0 + c) * W + i), acc[c]);
+          for (int c = 0; c < kRouterRT; ++c)
+            if (r0 + c < R) {
+              const float4 wv = ld4(rw + (size_t)(r0 + c) * W + i);
+              acc[c] = fmaf(xv.x, wv.x, acc[c]); acc[c] = fmaf(xv.y, wv.y, acc[c]);
+              acc[c] = fmaf(xv.z, wv.z, acc[c]); acc[c] = fmaf(xv.w, wv.w, acc[c]);
+            }
+        }
+      } else {
+        for (int i = l; i < W; i += 32) {
+          const float xv = xr[i];
+#pragma unroll
+          for (int c = 0; c < kRouterRT; ++c)
+            if (r0 + c < R) acc[c] = fmaf(xv, ldf<WT>(rw, (size_t)(r0 + c) * W + i), acc[c]);
+        }
       }
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < kRouterRT; ++c) {
         const float v = warp_sum(acc[c]);
         if (l == 0 && r0 + c < R) z[r0 + c] = v;
       }
@@ -170,7 +201,7 @@ template <typename WT>
 __global__ void __launch_bounds__(256) moe_expert_rows_kernel(const float* __restrict__ x, const bf16* __restrict__ xb,
                                                               const WT* __restrict__ w_gu, const WT* __restrict__ w_down,
                                                               const int32_t* __restrict__ ids, int E, int F, int W,
-                                                              float* __restrict__ y) {
+                                                              float* __restrict__ y, int packed) {
   extern __shared__ float sm[];
   const int t = blockIdx.x;
   const size_t item = (size_t)t * gridDim.y + blockIdx.y;  // (token, choice)
@@ -183,8 +214,9 @@ __global__ void __launch_bounds__(256) moe_expert_rows_kernel(const float* __res
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
   const WT* gu = w_gu + (size_t)e * 2 * F * W;
   for (int f = w; f < F; f += nw) {
-    const float g = warp_dot<WT>(gu + (size_t)f * W, xs, W, l);
-    const float u = warp_dot<WT>(gu + (size_t)(F + f) * W, xs, W, l);
+    const size_t gr = packed ? (size_t)(f >> 7) * 256 + (f & 127) : (size_t)f, ur = packed ? gr + 128 : (size_t)F + f;
+    const float g = warp_dot<WT>(gu + gr * W, xs, W, l);
+    const float u = warp_dot<WT>(gu + ur * W, xs, W, l);
     if (l == 0) {
       float v = g * sigmoidf_(g) * u;
       if (xb) v = __bfloat162float(__float2bfloat16(v));
@@ -317,12 +349,15 @@ cudaError_t stack_moe_init() {
   return cudaSuccess;
 }
 
-cudaError_t gated_unit(cudaStream_t s, const float* gu, long ldg, int act, float* out, bf16* outb, int T, int F) {
+cudaError_t gated_unit(cudaStream_t s, const float* gu, long ldg, int act, float* out, bf16* outb, int T, int F, bool packed) {
   if (T <= 0) return cudaSuccess;
+  if (packed && F % 128) return cudaErrorInvalidValue;
   const bool vec = F % 4 == 0 && ldg % 4 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)outb & 7) == 0;
   dim3 grid(T, ((vec ? F / 4 : F) + 255) / 256);
-  if (vec) gated_unit_kernel<4><<<grid, 256, 0, s>>>(gu, ldg, act, out, outb, F);
-  else gated_unit_kernel<1><<<grid, 256, 0, s>>>(gu, ldg, act, out, outb, F);
+  if (vec && packed) gated_unit_kernel<4, true><<<grid, 256, 0, s>>>(gu, ldg, act, out, outb, F);
+  else if (vec) gated_unit_kernel<4, false><<<grid, 256, 0, s>>>(gu, ldg, act, out, outb, F);
+  else if (packed) gated_unit_kernel<1, true><<<grid, 256, 0, s>>>(gu, ldg, act, out, outb, F);
+  else gated_unit_kernel<1, false><<<grid, 256, 0, s>>>(gu, ldg, act, out, outb, F);
   return cudaGetLastError();
 }
 
@@ -358,13 +393,13 @@ cudaError_t gated_unit_b16(cudaStream_t s, const bf16* gu, long ldg, int act, bf
 }
 
 cudaError_t moe_expert_rows(cudaStream_t s, const float* x, const bf16* xb, const void* w_gu, const void* w_down, bool f32,
-                            const int32_t* ids, int top_k, int E, int F, int W, float* y, int T) {
+                            const int32_t* ids, int top_k, int E, int F, int W, float* y, int T, bool packed) {
   if (T <= 0) return cudaSuccess;
   const size_t smem = ((size_t)(W + 3) / 4 * 4 + F) * 4;
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
   dim3 grid(T, top_k);
-  if (f32) moe_expert_rows_kernel<float><<<grid, 256, smem, s>>>(x, xb, (const float*)w_gu, (const float*)w_down, ids, E, F, W, y);
-  else moe_expert_rows_kernel<bf16><<<grid, 256, smem, s>>>(x, xb, (const bf16*)w_gu, (const bf16*)w_down, ids, E, F, W, y);
+  if (f32) moe_expert_rows_kernel<float><<<grid, 256, smem, s>>>(x, xb, (const float*)w_gu, (const float*)w_down, ids, E, F, W, y, packed ? 1 : 0);
+  else moe_expert_rows_kernel<bf16><<<grid, 256, smem, s>>>(x, xb, (const bf16*)w_gu, (const bf16*)w_down, ids, E, F, W, y, packed ? 1 : 0);
   return cudaGetLastError();
 }
 

@@ -97,6 +97,8 @@ CONFIGS = {
     # head sizes of the fused tensor-core attention with blocks shorter than its 64-key tiles / longer than a page
     "fused_attention_small_blocks": dict(width=128, heads=4, kv_heads=1, dim=64, rot_dims=64, chunk=20, order=("dense",)),
     "fused_attention_128": dict(width=128, vocab=256, heads=2, kv_heads=2, dim=128, rot_dims=32, chunk=70, order=("dense", None)),
+    # inner sizes that are multiples of 128: gate / up rows stored as [128 gate | 128 up] tiles, gated epilogue of the GEMM
+    "packed_gated_units": dict(width=128, vocab=256, heads=4, kv_heads=2, dim=64, rot_dims=32, chunk=96, ff=256, expert_ff=128),
     "tensor_core_shapes": dict(width=128, vocab=256, heads=4, kv_heads=2, dim=64, rot_dims=32, chunk=96, ff=128, expert_ff=64),
 }
 
@@ -113,8 +115,9 @@ def test_whole_prompt_matches_oracle(name, f32):
     check(got, want, ok, f32, least=0.0 if name == "layers_differ" else 0.15)
 
 
-def test_steps_of_hundreds_of_tokens_take_the_tensor_core_products():
-    cfg = ref.random_config(**CONFIGS["tensor_core_shapes"])
+@pytest.mark.parametrize("name", ["tensor_core_shapes", "packed_gated_units"])
+def test_steps_of_hundreds_of_tokens_take_the_tensor_core_products(name):
+    cfg = ref.random_config(**CONFIGS[name])
     sd = ref.random_state_dict(cfg, seed=5)
     toks = tokens(2, 420, cfg["vocab"])
     for f32 in (1, 0):
