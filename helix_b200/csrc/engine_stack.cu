@@ -94,6 +94,7 @@ int Engine::load_begin_stack(const hb_stack_desc& sd, const hb_layer_desc* layer
   if (model_.arena_bytes > budget_) return fail(HB_ERR_OOM, "weights alone exceed the memory budget");
   if (model_.arena_bytes > free_b) return fail(HB_ERR_OOM, "weights exceed free device memory");
   CU(cudaMalloc(&model_.arena, model_.arena_bytes));
+  CU(cudaMemset(model_.arena, 0, model_.arena_bytes));  // padding rows (routers below one MMA tile) must read as zero
   layout_stack(model_);
   load_open_ = true;
   return HB_OK;
@@ -238,7 +239,7 @@ size_t Engine::workspace_bytes_stack() const {
   if (dm.att > 0) b += al256(T * (size_t)up8(dm.att) * 2);
   if (dm.moe_r > 0) {
     const size_t rows = dm.moe_e > 0 ? (size_t)moe_group_max_rows((int)T * dm.moe_top, dm.moe_e) : T * (size_t)dm.moe_top;
-    b += al256(T * (size_t)up8(dm.moe_r) * 4) + 2 * al256(T * (size_t)dm.moe_top * 4) + al256(rows * W * 4);
+    b += al256(T * (size_t)std::max(64, up8(dm.moe_r)) * 4) + 2 * al256(T * (size_t)dm.moe_top * 4) + al256(rows * W * 4);
     if (dm.moe_e > 0)
       b += al256(T * (size_t)dm.moe_top * 4) + al256(rows * 4) + al256(rows / 128 * 4) + al256(rows * W * 2) + al256(rows * dm.moe_f * 2);
   }
@@ -317,7 +318,7 @@ int Engine::alloc_runtime_stack() {
     sk_.att16 = (bf16*)take(T * (size_t)sk_.ldatt * 2);
   }
   if (dm.moe_r > 0) {
-    sk_.ldz = up8(dm.moe_r);
+    sk_.ldz = std::max(64, up8(dm.moe_r));
     sk_.moe_z = (float*)take(T * (size_t)sk_.ldz * 4);
     sk_.moe_ids = (int32_t*)take(T * (size_t)dm.moe_top * 4);
     sk_.moe_w = (float*)take(T * (size_t)dm.moe_top * 4);
@@ -500,7 +501,9 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
     const StackLayerW& w = model_.sw[i];
     const int H = l.heads, Dk = l.dim, Dv = l.vdim;
     // every projection that reads the stream, in one GEMM
-    int rc = stack_gemm(k.x, x16, W, w.w_in, w.n_in, W, k.p1, k.ld1, T);
+    // (grouped-query layers keep the rows of this product dense: the buffer's stride is sized for the widest gated unit)
+    const int ldin = l.mixer == HB_MIXER_GQA ? up8(w.n_in) : k.ld1;
+    int rc = stack_gemm(k.x, x16, W, w.w_in, w.n_in, W, k.p1, ldin, T);
     if (rc != HB_OK) return rc;
     if (l.mixer == HB_MIXER_GLA) {
       // decay: z = a2 (a1 x) + b -> sigmoid(z)^(1/tau), fp32
@@ -522,7 +525,7 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       void* kplane = (uint8_t*)kv_ + plane_off_[w.cache_plane];
       void* vplane = (uint8_t*)kv_ + plane_off_[w.cache_plane_v];
       GqaPrepArgs pa{};
-      pa.p = k.p1; pa.ldp = k.ld1; pa.q_off = w.off_q; pa.k_off = w.off_k; pa.v_off = w.off_v;
+      pa.p = k.p1; pa.ldp = ldin; pa.q_off = w.off_q; pa.k_off = w.off_k; pa.v_off = w.off_v;
       // prompt portions (any entry of >= kAttDenseMin tokens): the whole step runs on the fused tcgen05 kernel over the paged
       // planes; steps of single tokens and short portions, other masks, head sizes and the exact mode take the per-token kernel
       bool fused = gqa_fused_ok(model_, l, cfg_.max_ctx) && k.att16 && k.q16 && (H * Dk) % 8 == 0 && page_ == 64;
@@ -542,7 +545,7 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
         fa.k = nullptr; fa.ldk = 0; fa.v = nullptr; fa.ldv = 0;
         const bool direct = stack_tc(W, H * Dv, H * Dv, W);  // the output projection reads the bf16 copy only
         fa.out = direct ? mo16 : k.att16; fa.ldo = H * Dv;
-        if (direct && (l.attn_flags & HB_ATTN_HEAD_GATE)) { fa.head_gate = k.p1 + w.off_g; fa.ldg = k.ld1; }
+        if (direct && (l.attn_flags & HB_ATTN_HEAD_GATE)) { fa.head_gate = k.p1 + w.off_g; fa.ldg = ldin; }
         fa.cu_seqlens = cu; fa.B = B; fa.T = T; fa.max_seqlen = longest;
         fa.Hq = H; fa.Hkv = G; fa.D = Dk; fa.causal = 1; fa.scale = l.scale;
         fa.k_cache = (const bf16*)kplane; fa.v_cache = (const bf16*)vplane;
@@ -553,14 +556,14 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
         SPAN(1, 2.0 * T * H * (double)std::min(l.window, cfg_.max_ctx) * (Dk + Dv) * 0.5, attn_prefill(stream_, fa));
         if (!direct)
           SPAN(3, 10.0 * T * H * Dv, head_gate_rows(stream_, k.att16, H * Dv, (l.attn_flags & HB_ATTN_HEAD_GATE) ? k.p1 + w.off_g : nullptr,
-                                                    k.ld1, k.mo, mo16, T, H, Dv));
+                                                    ldin, k.mo, mo16, T, H, Dv));
       } else {
       GqaAttnArgs aa{};
       aa.q = k.p2; aa.ldq = H * Dk;
       aa.k_cache = kplane; aa.v_cache = vplane; aa.f32 = f32;
       aa.page_table = pt; aa.max_pages = max_pages_per_seq_; aa.page_size = page_;
       aa.positions = positions; aa.seq_of = seqof;
-      aa.gate = (l.attn_flags & HB_ATTN_HEAD_GATE) ? k.p1 + w.off_g : nullptr; aa.ldg = k.ld1;
+      aa.gate = (l.attn_flags & HB_ATTN_HEAD_GATE) ? k.p1 + w.off_g : nullptr; aa.ldg = ldin;
       aa.out = k.mo; aa.ldo = H * Dv; aa.out_b16 = mo16;
       aa.T = T; aa.H = H; aa.G = G; aa.D = Dk; aa.Dv = Dv; aa.mask = l.mask; aa.window = l.window;
       aa.unit_sink = (l.attn_flags & HB_ATTN_UNIT_SINK) != 0; aa.scale = l.scale;
@@ -665,7 +668,13 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
     if (l.ff > 0 && l.ff_kind == HB_FF_MOE) {
       // router in fp32 on the stream itself; experts per (token, choice); identity outputs and weights in the combination
       const int E = l.experts, R = l.experts + l.identity_experts, F = l.ff;
-      if (moe_router_smem(R, W, f32) <= 200 * 1024) {
+      if (T > 256 && R <= 64 && stack_tc(64, W, W, k.ldz) && k.ldz >= 64) {
+        // steps of many tokens: logits on the tensor cores from the bf16 copy of the stream (fp32 accumulation; the router's
+        // rows are padded with zero rows to one MMA tile), then the choice in fp32
+        GemmArgs g{x16, W, (const bf16*)w.router, W, k.moe_z, k.ldz, nullptr, 0, nullptr, T, 64, W, EPI_F32, 0};
+        SPAN(0, 2.0 * T * 64 * W, gemm_bf16_tn(stream_, g));
+        SPAN(3, 8.0 * T * R, moe_route(stream_, k.moe_z, k.ldz, w.correction, f32, R, l.top_k, k.moe_ids, k.moe_w, T));
+      } else if (moe_router_smem(R, W, f32) <= 200 * 1024) {
         SPAN(3, 4.0 * T * W, moe_router(stream_, k.x, w.router, w.correction, f32, R, W, l.top_k, k.moe_ids, k.moe_w, T,
                                         cfg_.sm_budget > 0 ? cfg_.sm_budget : 148));
       } else {  // a router too large for shared memory: product, then choice

@@ -2,6 +2,8 @@
 
 #include <math.h>
 
+#include <algorithm>
+
 namespace hb {
 
 namespace {
@@ -369,7 +371,7 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
     if (l.ff > 0 && l.ff_kind == HB_FF_MOE) {
       const size_t Fn = l.ff, E = l.experts, R = (size_t)l.experts + l.identity_experts;
       uint8_t* n2 = take(W);
-      uint8_t* router = take(R * W);
+      uint8_t* router = take(std::max<size_t>(R, 64) * W);  // at least one MMA tile of rows; the arena is zeroed at load
       uint8_t* corr = take(R);
       uint8_t* gu = take(E * 2 * Fn * W);
       uint8_t* dn = take(E * W * Fn);

@@ -2,8 +2,8 @@
 // ([page][kv_head][page_size][D | Dv], bf16 or fp32): rotation + unit normalisation + cache write of a step's tokens, and the
 // attention of every token of a step — single decoded tokens and prompt portions alike — under a sliding-window, block
 // ("chunk") or causal mask, optionally with one extra unit in the softmax denominator and a sigmoid gate per head.
-// Softmax, normalisation and every sum are fp32; rotation angles are formed in double precision (position * frequency loses
-// bits that matter at positions in the thousands).  Summation orders are fixed per output element: a position's result does
+// Softmax, normalisation and every sum are fp32; rotation angles are formed and reduced to one turn in double precision
+// (position * frequency loses bits that matter at positions in the thousands).  Summation orders are fixed per output element: a position's result does
 // not depend on what else the step carries.
 #include <math.h>
 
@@ -16,36 +16,62 @@
 namespace hb {
 namespace {
 
-constexpr int kPrepThreads = 128;
+// One warp per run of kPrepUnits (token, head) units — query heads, then key heads (a key head's unit also writes the value
+// row).  Warps are independent (no block-wide phase) and issue the loads of all their units before they work on the first,
+// so an SM keeps hundreds of rows in flight.  A lane forms the angle of its pair itself: pos * f and its reduction to one
+// turn in fp64 (four operations), sine and cosine of the remainder in fp32.
+constexpr int kPrepWarps = 8;
+constexpr int kPrepUnits = 4;
 
 template <typename CT>
-__global__ void __launch_bounds__(kPrepThreads) gqa_prep_kernel(GqaPrepArgs a) {
+__global__ void __launch_bounds__(kPrepWarps * 32) gqa_prep_kernel(GqaPrepArgs a) {
   extern __shared__ float sm[];
   const int half = a.rope_dims / 2, Dp = (a.D + 3) / 4 * 4;
-  float* cs = sm;                                  // [half][2]: cos, sin of this token's angles
-  float* bufs = sm + ((2 * half + 3) / 4 * 4);     // one row buffer per warp
-  const int t = blockIdx.x, pos = a.positions[t];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    double s, c;
-    sincos((double)pos * a.freqs[i], &s, &c);
-    cs[2 * i] = (float)c;
-    cs[2 * i + 1] = (float)s;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per_tok = a.H + a.G;
+  const long total = (long)a.T * per_tok;
+  const long unit0 = ((long)blockIdx.x * kPrepWarps + warp) * kPrepUnits;
+  if (unit0 >= total) return;
+  float* bufs = sm + (size_t)warp * kPrepUnits * Dp;
+  // 16-byte loads when every head row starts on a 16-byte boundary
+  const bool vec = (a.D & 3) == 0 && (a.ldp & 3) == 0 && (a.q_off & 3) == 0 && (a.k_off & 3) == 0 && ((uintptr_t)a.p & 15) == 0;
+#pragma unroll
+  for (int k = 0; k < kPrepUnits; ++k) {
+    const long unit = unit0 + k;
+    if (unit >= total) break;
+    const int t = (int)(unit / per_tok), u = (int)(unit % per_tok);
+    const float* src = a.p + (size_t)t * a.ldp + (u < a.H ? a.q_off + (size_t)u * a.D : a.k_off + (size_t)(u - a.H) * a.D);
+    float* buf = bufs + k * Dp;
+    if (vec) {
+      for (int i = lane * 4; i < a.D; i += 128) *reinterpret_cast<float4*>(buf + i) = *reinterpret_cast<const float4*>(src + i);
+    } else {
+      for (int i = lane; i < a.D; i += 32) buf[i] = src[i];
+    }
   }
-  __syncthreads();
-  const int slot = a.slots ? a.slots[t] : -1;
-  const size_t page = slot >= 0 ? slot / a.page_size : 0, off = slot >= 0 ? slot % a.page_size : 0;
-  const float* prow = a.p + (size_t)t * a.ldp;
-  float* buf = bufs + warp * Dp;
-  for (int u = warp; u < a.H + a.G; u += nw) {
+  __syncwarp();
+  for (int k = 0; k < kPrepUnits; ++k) {
+    const long unit = unit0 + k;
+    if (unit >= total) break;
+    const int t = (int)(unit / per_tok), u = (int)(unit % per_tok);
+    const int pos = a.positions[t];
+    const int slot = a.slots ? a.slots[t] : -1;
+    const size_t page = slot >= 0 ? slot / a.page_size : 0, off = slot >= 0 ? slot % a.page_size : 0;
     const bool isq = u < a.H;
     const int head = isq ? u : u - a.H;
-    const float* src = prow + (isq ? a.q_off : a.k_off) + (size_t)head * a.D;
-    for (int i = lane; i < a.D; i += 32) buf[i] = src[i];
-    __syncwarp();
+    float* buf = bufs + k * Dp;
+    if (!isq && slot >= 0) {  // values leave the projection untouched
+      const float* vsrc = a.v_off == a.k_off && a.Dv == a.D ? buf : a.p + (size_t)t * a.ldp + a.v_off + (size_t)head * a.Dv;
+      CT* vrow = (CT*)a.v_cache + ((page * a.G + head) * a.page_size + off) * a.Dv;
+      for (int i = lane; i < a.Dv; i += 32) stf<CT>(vrow, i, vsrc[i]);
+      __syncwarp();
+    }
     for (int i = lane; i < half; i += 32) {
+      const double ang = (double)pos * a.freqs[i];
+      const double red = fma(-6.283185307179586476925, rint(ang * 0.15915494309189533577), ang);
+      float s, c;
+      sincosf((float)red, &s, &c);
       const int i0 = a.pairing ? 2 * i : i, i1 = a.pairing ? 2 * i + 1 : i + half;
-      const float x = buf[i0], y = buf[i1], c = cs[2 * i], s = cs[2 * i + 1];
+      const float x = buf[i0], y = buf[i1];
       buf[i0] = x * c - y * s;
       buf[i1] = y * c + x * s;
     }
@@ -69,13 +95,85 @@ __global__ void __launch_bounds__(kPrepThreads) gqa_prep_kernel(GqaPrepArgs a) {
       CT* row = (CT*)a.k_cache + ((page * a.G + head) * a.page_size + off) * a.D;
       for (int i = lane; i < a.D; i += 32) stf<CT>(row, i, buf[i] * rs);
     }
-    __syncwarp();
   }
-  if (slot >= 0) {  // values leave the projection untouched
-    for (int e = threadIdx.x; e < a.G * a.Dv; e += blockDim.x) {
-      const int head = e / a.Dv, i = e % a.Dv;
-      CT* row = (CT*)a.v_cache + ((page * a.G + head) * a.page_size + off) * a.Dv;
-      stf<CT>(row, i, prow[a.v_off + (size_t)head * a.Dv + i]);
+}
+
+// The same step for the common layout — neighbouring pairs (2i, 2i+1), head rows that start on 16-byte boundaries, values
+// that are the keys: a lane owns four consecutive entries (two pairs) of a head row in registers; no shared memory, one
+// 16-byte load and one 8- or 16-byte store per lane and row.  One warp per (token, head) unit; D <= 512.
+template <typename CT>
+__global__ void __launch_bounds__(256) gqa_prep_vec_kernel(GqaPrepArgs a) {
+  const int lane = threadIdx.x & 31;
+  const unsigned unit = blockIdx.x * 8u + (threadIdx.x >> 5);
+  const unsigned per_tok = a.H + a.G;
+  if (unit >= (unsigned)a.T * per_tok) return;
+  const int t = unit / per_tok, u = unit % per_tok;
+  const bool isq = u < a.H;
+  const int head = isq ? u : u - a.H;
+  const int pos = a.positions[t], half = a.rope_dims / 2;
+  const float* src = a.p + (size_t)t * a.ldp + (isq ? a.q_off : a.k_off) + (size_t)head * a.D;
+  float4 v[4];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int e = 4 * lane + 128 * j;
+    v[j] = e < a.D ? *reinterpret_cast<const float4*>(src + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  const int slot = (!isq && a.slots) ? a.slots[t] : -1;
+  const size_t rowi = slot >= 0 ? ((size_t)(slot / a.page_size) * a.G + head) * a.page_size + slot % a.page_size : 0;
+  auto put16 = [](bf16* row, int e, const float4& x) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
+    uint2 pk;
+    pk.x = *reinterpret_cast<unsigned*>(&lo);
+    pk.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(row + e) = pk;
+  };
+  auto put = [&](CT* row, int e, const float4& x) {
+    if (sizeof(CT) == 4) *reinterpret_cast<float4*>(reinterpret_cast<float*>(row) + e) = x;
+    else put16(reinterpret_cast<bf16*>(row), e, x);
+  };
+  if (slot >= 0) {  // values: the key projection as it is
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int e = 4 * lane + 128 * j;
+      if (e < a.D) put((CT*)a.v_cache + rowi * a.Dv, e, v[j]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int e = 4 * lane + 128 * j;
+    if (e < a.D) {
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const int pr = e / 2 + h2;
+        if (pr < half) {
+          const double ang = (double)pos * a.freqs[pr];
+          const double red = fma(-6.283185307179586476925, rint(ang * 0.15915494309189533577), ang);
+          float sn, cs;
+          sincosf((float)red, &sn, &cs);
+          float& x = h2 ? v[j].z : v[j].x;
+          float& y = h2 ? v[j].w : v[j].y;
+          const float x0 = x, y0 = y;
+          x = x0 * cs - y0 * sn;
+          y = y0 * cs + x0 * sn;
+        }
+      }
+      ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+    }
+  }
+  float rs = 1.f;
+  if (a.unit_norm) rs = 1.f / sqrtf(warp_sum(ss) / (float)a.D + a.eps);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int e = 4 * lane + 128 * j;
+    if (e >= a.D) continue;
+    const float4 o = make_float4(v[j].x * rs, v[j].y * rs, v[j].z * rs, v[j].w * rs);
+    if (isq) {
+      const size_t at = (size_t)t * a.ldq + (size_t)head * a.D;
+      if (a.q) *reinterpret_cast<float4*>(a.q + at + e) = o;
+      if (a.q_b16) put16(a.q_b16 + at, e, o);
+    } else if (slot >= 0) {
+      put((CT*)a.k_cache + rowi * a.D, e, o);
     }
   }
 }
@@ -361,15 +459,29 @@ cudaError_t stack_gqa_init() {
   const int big = 200 * 1024;
   if ((e = cudaFuncSetAttribute(gqa_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big)) != cudaSuccess) return e;
   if ((e = cudaFuncSetAttribute(gqa_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(gqa_prep_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(gqa_prep_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024)) != cudaSuccess) return e;
   return cudaSuccess;
 }
 
 cudaError_t gqa_prep(cudaStream_t s, const GqaPrepArgs& a) {
   if (a.T <= 0) return cudaSuccess;
   if (a.rope_dims % 2 || a.rope_dims > a.D || (a.rope_dims > 0 && !a.freqs)) return cudaErrorInvalidValue;
-  const size_t smem = ((size_t)(a.rope_dims + 3) / 4 * 4 + (size_t)(kPrepThreads / 32) * ((a.D + 3) / 4 * 4)) * 4;
-  if (a.f32) gqa_prep_kernel<float><<<a.T, kPrepThreads, smem, s>>>(a);
-  else gqa_prep_kernel<bf16><<<a.T, kPrepThreads, smem, s>>>(a);
+  const bool aligned = (a.D & 3) == 0 && a.D <= 512 && (a.ldp & 3) == 0 && (a.q_off & 3) == 0 && (a.k_off & 3) == 0 && (a.ldq & 3) == 0 &&
+                       ((uintptr_t)a.p & 15) == 0 && ((uintptr_t)a.q & 15) == 0 && ((uintptr_t)a.q_b16 & 7) == 0 &&
+                       ((uintptr_t)a.k_cache & 15) == 0 && ((uintptr_t)a.v_cache & 15) == 0;
+  if (aligned && (a.pairing == 1 || a.rope_dims == 0) && a.v_off == a.k_off && a.Dv == a.D) {
+    const unsigned blocks = (unsigned)(((long)a.T * (a.H + a.G) + 7) / 8);
+    if (a.f32) gqa_prep_vec_kernel<float><<<blocks, 256, 0, s>>>(a);
+    else gqa_prep_vec_kernel<bf16><<<blocks, 256, 0, s>>>(a);
+    return cudaGetLastError();
+  }
+  const size_t smem = (size_t)kPrepWarps * kPrepUnits * ((a.D + 3) / 4 * 4) * 4;
+  if (smem > 72 * 1024) return cudaErrorInvalidValue;
+  const long units = (long)a.T * (a.H + a.G);
+  const unsigned grid = (unsigned)((units + kPrepWarps * kPrepUnits - 1) / (kPrepWarps * kPrepUnits));
+  if (a.f32) gqa_prep_kernel<float><<<grid, kPrepWarps * 32, smem, s>>>(a);
+  else gqa_prep_kernel<bf16><<<grid, kPrepWarps * 32, smem, s>>>(a);
   return cudaGetLastError();
 }
 

@@ -156,6 +156,34 @@ __global__ void __launch_bounds__(kRouterWarps * 32) moe_router_kernel(const flo
   }
 }
 
+// Steps of few tokens: one block per token, warp w forms the outputs w, w + warps, ... straight from the router's rows in
+// global memory (each row is read once per block), warp 0 chooses.  dynamic smem: logits [R] + scratch [R]
+template <typename WT>
+__global__ void __launch_bounds__(kRouterWarps * 32) moe_router_small_kernel(const float* __restrict__ x, const WT* __restrict__ router,
+                                                                             const WT* __restrict__ corr, int R, int W, int top_k,
+                                                                             int32_t* __restrict__ ids, float* __restrict__ wts) {
+  extern __shared__ float sm[];
+  const int t = blockIdx.x, w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  const float* xr = x + (size_t)t * W;
+  const bool vec = (W & 3) == 0 && ((uintptr_t)router & 15) == 0;
+  for (int r = w; r < R; r += kRouterWarps) {
+    const WT* row = router + (size_t)r * W;
+    float acc = 0.f;
+    if (vec) {
+      for (int i = l * 4; i < W; i += 128) {
+        const float4 xv = ld4(xr + i), wv = ld4(row + i);
+        acc = fmaf(xv.x, wv.x, acc); acc = fmaf(xv.y, wv.y, acc); acc = fmaf(xv.z, wv.z, acc); acc = fmaf(xv.w, wv.w, acc);
+      }
+    } else {
+      for (int i = l; i < W; i += 32) acc = fmaf(xr[i], ldf<WT>(row, i), acc);
+    }
+    acc = warp_sum(acc);
+    if (l == 0) sm[r] = acc;
+  }
+  __syncthreads();
+  if (w == 0) route_one<WT>(sm, corr, R, top_k, sm + R, ids + (size_t)t * top_k, wts + (size_t)t * top_k, l);
+}
+
 // bf16 in, bf16 out: h[t, j] = act(gu[t, j]) * gu[t, F + j], eight columns per thread (F and ldg multiples of eight)
 __global__ void gated_unit_b16_kernel(const bf16* __restrict__ gu, long ldg, int act, bf16* __restrict__ out, int F) {
   const size_t t = blockIdx.x;
@@ -377,8 +405,15 @@ size_t moe_router_smem(int R, int W, bool f32) {
 cudaError_t moe_router(cudaStream_t s, const float* x, const void* router, const void* corr, bool f32, int R, int W, int top_k,
                        int32_t* ids, float* wts, int T, int sms) {
   if (T <= 0) return cudaSuccess;
+  if (R <= 0 || top_k <= 0 || top_k > R) return cudaErrorInvalidValue;
+  if (T <= 2 * (sms > 0 ? sms : 148) && R <= 4096) {  // few tokens: a block per token, no staging of the router
+    const size_t sm_small = (size_t)2 * R * 4;
+    if (f32) moe_router_small_kernel<float><<<T, kRouterWarps * 32, sm_small, s>>>(x, (const float*)router, (const float*)corr, R, W, top_k, ids, wts);
+    else moe_router_small_kernel<bf16><<<T, kRouterWarps * 32, sm_small, s>>>(x, (const bf16*)router, (const bf16*)corr, R, W, top_k, ids, wts);
+    return cudaGetLastError();
+  }
   const size_t smem = moe_router_smem(R, W, f32);
-  if (R <= 0 || top_k <= 0 || top_k > R || smem > 200 * 1024) return cudaErrorInvalidValue;
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;
   const int grid = std::max(1, std::min((T + kRouterWarps - 1) / kRouterWarps, sms > 0 ? sms : 148));
   if (f32) moe_router_kernel<float><<<grid, kRouterWarps * 32, smem, s>>>(x, (const float*)router, (const float*)corr, R, W, top_k, ids, wts, T);
   else moe_router_kernel<bf16><<<grid, kRouterWarps * 32, smem, s>>>(x, (const bf16*)router, (const bf16*)corr, R, W, top_k, ids, wts, T);

@@ -99,6 +99,7 @@ CONFIGS = {
     "fused_attention_128": dict(width=128, vocab=256, heads=2, kv_heads=2, dim=128, rot_dims=32, chunk=70, order=("dense", None)),
     # inner sizes that are multiples of 128: gate / up rows stored as [128 gate | 128 up] tiles, gated epilogue of the GEMM
     "packed_gated_units": dict(width=128, vocab=256, heads=4, kv_heads=2, dim=64, rot_dims=32, chunk=96, ff=256, expert_ff=128),
+    "widest_heads": dict(width=64, heads=2, kv_heads=1, dim=512, rot_dims=128, chunk=33, order=(None,), scale=0.05),
     "tensor_core_shapes": dict(width=128, vocab=256, heads=4, kv_heads=2, dim=64, rot_dims=32, chunk=96, ff=128, expert_ff=64),
 }
 
