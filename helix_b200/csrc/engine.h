@@ -208,7 +208,12 @@ class Engine {
     int32_t *moe_row_of = nullptr, *moe_src = nullptr, *moe_tiles = nullptr;
     bf16 *moe_a16 = nullptr, *moe_h16 = nullptr;
     bf16* gu16 = nullptr;  // [gate | up] products of a gated unit as bf16 (tensor-core path of steps of > 256 tokens, experts)
-    std::vector<const double*> freqs;  // per layer: rotation frequencies of a grouped-query layer (device), else null
+    // rotation of grouped-query layers: distinct frequency sets (device, fp64; layers with equal rotation share one), the
+    // step's cos / sin table of every set, and each layer's set (-1: none)
+    std::vector<const double*> freq_sets;
+    std::vector<int> freq_half;
+    std::vector<float*> rope_cs;
+    std::vector<int> layer_set;
   } sk_{};
   struct StepEntry { int t0, first, n; };  // host copy of the step's entries: first packed row, first position, tokens
   std::vector<StepEntry> step_entries_;

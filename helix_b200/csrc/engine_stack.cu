@@ -235,7 +235,7 @@ size_t Engine::workspace_bytes_stack() const {
   const StackDims dm = stack_dims(model_, cfg_.max_ctx);
   const int n1 = dm.n1, n2 = dm.n2, q = dm.q, qa = dm.qa, cx = dm.cx, mo = dm.mo;
   size_t b = 0;
-  b += al256((size_t)std::max(dm.rope_half, 1) * 8);
+  b += al256((size_t)std::max(dm.rope_half, 1) * 8) + al256(T * 2 * (size_t)std::max(dm.rope_half, 1) * 4);
   if (dm.att > 0) b += al256(T * (size_t)up8(dm.att) * 2);
   if (dm.moe_r > 0) {
     const size_t rows = dm.moe_e > 0 ? (size_t)moe_group_max_rows((int)T * dm.moe_top, dm.moe_e) : T * (size_t)dm.moe_top;
@@ -302,15 +302,26 @@ int Engine::alloc_runtime_stack() {
   const int n1 = dm.n1, n2 = dm.n2, q = dm.q, qa = dm.qa, cx = dm.cx, mo = dm.mo;
   {  // rotation frequencies of the grouped-query layers (double precision, formed on the host)
     double* fq = (double*)take((size_t)std::max(dm.rope_half, 1) * 8);
-    sk_.freqs.assign(sd.n_layers, nullptr);
+    float* cs = (float*)take(T * 2 * (size_t)std::max(dm.rope_half, 1) * 4);
+    sk_.layer_set.assign(sd.n_layers, -1);
+    sk_.freq_sets.clear(); sk_.freq_half.clear(); sk_.rope_cs.clear();
+    std::vector<std::vector<double>> sets;
     size_t at = 0;
     for (int i = 0; i < sd.n_layers; ++i) {
       const hb_layer_desc& l = model_.sl[i];
       if (l.mixer != HB_MIXER_GQA || l.rope_dims <= 0) continue;
       const std::vector<double> f = stack_rope_freqs(l);
-      CU(cudaMemcpy(fq + at, f.data(), f.size() * 8, cudaMemcpyHostToDevice));
-      sk_.freqs[i] = fq + at;
-      at += f.size();
+      size_t sidx = 0;
+      while (sidx < sets.size() && sets[sidx] != f) ++sidx;
+      if (sidx == sets.size()) {
+        CU(cudaMemcpy(fq + at, f.data(), f.size() * 8, cudaMemcpyHostToDevice));
+        sets.push_back(f);
+        sk_.freq_sets.push_back(fq + at);
+        sk_.freq_half.push_back((int)f.size());
+        sk_.rope_cs.push_back(cs + T * 2 * at);
+        at += f.size();
+      }
+      sk_.layer_set[i] = (int)sidx;
     }
   }
   if (dm.att > 0) {
@@ -496,6 +507,8 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
   };
   SPAN(3, rowb, embed_rows_f32(stream_, tokens, model_.s_embed, f32, k.x, x16, T, W));
   if (sd.embed_norm) SPAN(3, 2 * rowb, norm_rows_f32(stream_, k.x, nullptr, model_.s_embed_norm, f32, goff, sd.norm_eps, k.x, x16, T, W));
+  for (size_t si = 0; si < k.freq_sets.size(); ++si)  // cos / sin of the step's positions, once per distinct rotation
+    SPAN(3, 8.0 * T * k.freq_half[si], stack_rope_table(stream_, positions, k.freq_sets[si], k.freq_half[si], k.rope_cs[si], T));
   for (int i = 0; i < sd.n_layers; ++i) {
     const hb_layer_desc& l = model_.sl[i];
     const StackLayerW& w = model_.sw[i];
@@ -535,7 +548,7 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       pa.q = fused ? nullptr : k.p2; pa.ldq = H * Dk; pa.q_b16 = fused ? k.q16 : nullptr;
       pa.k_cache = kplane; pa.v_cache = vplane; pa.f32 = f32;
       pa.slots = slots; pa.positions = positions;
-      pa.freqs = k.freqs[i]; pa.rope_dims = l.rope_dims; pa.pairing = l.rope_pairing;
+      pa.cs = k.layer_set[i] >= 0 ? k.rope_cs[k.layer_set[i]] : nullptr; pa.rope_dims = l.rope_dims; pa.pairing = l.rope_pairing;
       pa.H = H; pa.G = G; pa.D = Dk; pa.Dv = Dv; pa.page_size = page_;
       pa.unit_norm = (l.attn_flags & HB_ATTN_QK_UNIT_NORM) != 0; pa.eps = sd.norm_eps; pa.T = T;
       SPAN(3, 8.0 * T * (H + 2 * G) * Dk, gqa_prep(stream_, pa));

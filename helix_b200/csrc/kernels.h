@@ -358,8 +358,8 @@ cudaError_t to_bf16_rows(cudaStream_t s, const float* src, long lds, bf16* dst, 
 cudaError_t stack_gqa_init();
 enum StackMask : int { MASK_WINDOW = 0, MASK_CHUNK = 1, MASK_CAUSAL = 2 };  // == hb_mask
 // From the fused projection p[t] = [q (H*D) | k (G*D) | v (G*Dv, or the k columns again) | ...]: the first rope_dims entries of
-// every q and k head turn by pos * freqs[i] (pairing 1: entries (2i, 2i+1); 0: (i, i + rope_dims/2); angles in double
-// precision), then q and k are divided by their root mean square over D when unit_norm.  q goes to q[t, h*D..] and / or its
+// every q and k head turn by the angles of the step's table cs (pairing 1: entries (2i, 2i+1); 0: (i, i + rope_dims/2)),
+// then q and k are divided by their root mean square over D when unit_norm.  q goes to q[t, h*D..] and / or its
 // bf16 copy (either may be null),
 // k and the UNTOUCHED v columns to the cache rows of slots[t] (slot < 0: no cache write).
 struct GqaPrepArgs {
@@ -367,12 +367,16 @@ struct GqaPrepArgs {
   float* q; long ldq; bf16* q_b16;
   void* k_cache; void* v_cache; bool f32;
   const int32_t* slots; const int32_t* positions;
-  const double* freqs; int rope_dims, pairing;
+  const float* cs; int rope_dims, pairing;   // cs[t][2i], cs[t][2i+1] = cos, sin of positions[t] * f_i (stack_rope_table)
   int H, G, D, Dv, page_size;
   bool unit_norm; float eps;
   int T;
 };
 cudaError_t gqa_prep(cudaStream_t s, const GqaPrepArgs& a);
+// cs[t][2i] = cos(a), cs[t][2i+1] = sin(a), a = positions[t] * freqs[i], i < half: the angle and its reduction to one turn in
+// double precision, sine and cosine of the remainder in fp32.  Once per step and per distinct frequency set, shared by every
+// layer and head that rotates with it.
+cudaError_t stack_rope_table(cudaStream_t s, const int32_t* positions, const double* freqs, int half, float* cs, int T);
 // out[t, h, :] = gate_h * sum_j p_j v_j over the keys position pos_t sees, p_j = exp(s_j) / (sum_i exp(s_i) + sink),
 // s_j = scale * q[t, h] . k_j (head h reads kv head h / (H / G)).  Visible keys: mask 0 (window) pos - window < j <= pos;
 // 1 (chunk) j <= pos in the block of `window` positions that holds pos; 2 (causal) j <= pos.  sink = 1 when unit_sink

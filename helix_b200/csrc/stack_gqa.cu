@@ -3,7 +3,7 @@
 // attention of every token of a step — single decoded tokens and prompt portions alike — under a sliding-window, block
 // ("chunk") or causal mask, optionally with one extra unit in the softmax denominator and a sigmoid gate per head.
 // Softmax, normalisation and every sum are fp32; rotation angles are formed and reduced to one turn in double precision
-// (position * frequency loses bits that matter at positions in the thousands).  Summation orders are fixed per output element: a position's result does
+// (position * frequency loses bits that matter at positions in the thousands), once per step in a cos / sin table.  Summation orders are fixed per output element: a position's result does
 // not depend on what else the step carries.
 #include <math.h>
 
@@ -18,8 +18,7 @@ namespace {
 
 // One warp per run of kPrepUnits (token, head) units — query heads, then key heads (a key head's unit also writes the value
 // row).  Warps are independent (no block-wide phase) and issue the loads of all their units before they work on the first,
-// so an SM keeps hundreds of rows in flight.  A lane forms the angle of its pair itself: pos * f and its reduction to one
-// turn in fp64 (four operations), sine and cosine of the remainder in fp32.
+// so an SM keeps hundreds of rows in flight.  Cosines and sines come from the step's table (stack_rope_table).
 constexpr int kPrepWarps = 8;
 constexpr int kPrepUnits = 4;
 
@@ -53,7 +52,6 @@ __global__ void __launch_bounds__(kPrepWarps * 32) gqa_prep_kernel(GqaPrepArgs a
     const long unit = unit0 + k;
     if (unit >= total) break;
     const int t = (int)(unit / per_tok), u = (int)(unit % per_tok);
-    const int pos = a.positions[t];
     const int slot = a.slots ? a.slots[t] : -1;
     const size_t page = slot >= 0 ? slot / a.page_size : 0, off = slot >= 0 ? slot % a.page_size : 0;
     const bool isq = u < a.H;
@@ -66,10 +64,8 @@ __global__ void __launch_bounds__(kPrepWarps * 32) gqa_prep_kernel(GqaPrepArgs a
       __syncwarp();
     }
     for (int i = lane; i < half; i += 32) {
-      const double ang = (double)pos * a.freqs[i];
-      const double red = fma(-6.283185307179586476925, rint(ang * 0.15915494309189533577), ang);
-      float s, c;
-      sincosf((float)red, &s, &c);
+      const float2 sc2 = *reinterpret_cast<const float2*>(a.cs + (size_t)t * a.rope_dims + 2 * i);
+      const float c = sc2.x, s = sc2.y;
       const int i0 = a.pairing ? 2 * i : i, i1 = a.pairing ? 2 * i + 1 : i + half;
       const float x = buf[i0], y = buf[i1];
       buf[i0] = x * c - y * s;
@@ -110,7 +106,7 @@ __global__ void __launch_bounds__(256) gqa_prep_vec_kernel(GqaPrepArgs a) {
   const int t = unit / per_tok, u = unit % per_tok;
   const bool isq = u < a.H;
   const int head = isq ? u : u - a.H;
-  const int pos = a.positions[t], half = a.rope_dims / 2;
+  const int half = a.rope_dims / 2;
   const float* src = a.p + (size_t)t * a.ldp + (isq ? a.q_off : a.k_off) + (size_t)head * a.D;
   float4 v[4];
   float ss = 0.f;
@@ -143,14 +139,20 @@ __global__ void __launch_bounds__(256) gqa_prep_vec_kernel(GqaPrepArgs a) {
   for (int j = 0; j < 4; ++j) {
     const int e = 4 * lane + 128 * j;
     if (e < a.D) {
+      // the lane's two pairs are neighbours in the table: cos, sin, cos, sin (rope_dims is even; a 16-byte load when both rotate)
+      float c4[4] = {1.f, 0.f, 1.f, 0.f};
+      if (e / 2 + 1 < half) {
+        const float4 tq = *reinterpret_cast<const float4*>(a.cs + (size_t)t * a.rope_dims + e);
+        c4[0] = tq.x; c4[1] = tq.y; c4[2] = tq.z; c4[3] = tq.w;
+      } else if (e / 2 < half) {
+        const float2 tq = *reinterpret_cast<const float2*>(a.cs + (size_t)t * a.rope_dims + e);
+        c4[0] = tq.x; c4[1] = tq.y;
+      }
 #pragma unroll
       for (int h2 = 0; h2 < 2; ++h2) {
         const int pr = e / 2 + h2;
         if (pr < half) {
-          const double ang = (double)pos * a.freqs[pr];
-          const double red = fma(-6.283185307179586476925, rint(ang * 0.15915494309189533577), ang);
-          float sn, cs;
-          sincosf((float)red, &sn, &cs);
+          const float cs = c4[2 * h2], sn = c4[2 * h2 + 1];
           float& x = h2 ? v[j].z : v[j].x;
           float& y = h2 ? v[j].w : v[j].y;
           const float x0 = x, y0 = y;
@@ -440,7 +442,25 @@ __global__ void head_gate_kernel(const bf16* __restrict__ o, long ldo, const flo
   }
 }
 
+__global__ void rope_table_kernel(const int32_t* __restrict__ positions, const double* __restrict__ freqs, int half,
+                                  float* __restrict__ cs, int T) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long)T * half) return;
+  const int t = (int)(idx / half), i = (int)(idx % half);
+  const double ang = (double)positions[t] * freqs[i];
+  const double red = fma(-6.283185307179586476925, rint(ang * 0.15915494309189533577), ang);
+  float s, c;
+  sincosf((float)red, &s, &c);
+  *reinterpret_cast<float2*>(cs + 2 * idx) = make_float2(c, s);
+}
+
 }  // namespace
+
+cudaError_t stack_rope_table(cudaStream_t s, const int32_t* positions, const double* freqs, int half, float* cs, int T) {
+  if (T <= 0 || half <= 0) return cudaSuccess;
+  rope_table_kernel<<<(unsigned)(((long)T * half + 255) / 256), 256, 0, s>>>(positions, freqs, half, cs, T);
+  return cudaGetLastError();
+}
 
 cudaError_t head_gate_rows(cudaStream_t s, const bf16* o, long ldo, const float* gate, long ldg, float* out, bf16* outb, int T, int H,
                            int Dv) {
@@ -466,10 +486,11 @@ cudaError_t stack_gqa_init() {
 
 cudaError_t gqa_prep(cudaStream_t s, const GqaPrepArgs& a) {
   if (a.T <= 0) return cudaSuccess;
-  if (a.rope_dims % 2 || a.rope_dims > a.D || (a.rope_dims > 0 && !a.freqs)) return cudaErrorInvalidValue;
+  if (a.rope_dims % 2 || a.rope_dims > a.D || (a.rope_dims > 0 && !a.cs)) return cudaErrorInvalidValue;
   const bool aligned = (a.D & 3) == 0 && a.D <= 512 && (a.ldp & 3) == 0 && (a.q_off & 3) == 0 && (a.k_off & 3) == 0 && (a.ldq & 3) == 0 &&
                        ((uintptr_t)a.p & 15) == 0 && ((uintptr_t)a.q & 15) == 0 && ((uintptr_t)a.q_b16 & 7) == 0 &&
-                       ((uintptr_t)a.k_cache & 15) == 0 && ((uintptr_t)a.v_cache & 15) == 0;
+                       ((uintptr_t)a.k_cache & 15) == 0 && ((uintptr_t)a.v_cache & 15) == 0 && ((uintptr_t)a.cs & 15) == 0 &&
+                       (a.rope_dims & 3) == 0;
   if (aligned && (a.pairing == 1 || a.rope_dims == 0) && a.v_off == a.k_off && a.Dv == a.D) {
     const unsigned blocks = (unsigned)(((long)a.T * (a.H + a.G) + 7) / 8);
     if (a.f32) gqa_prep_vec_kernel<float><<<blocks, 256, 0, s>>>(a);
