@@ -74,7 +74,7 @@ def risepel_stack(width, layers, ff=None, window=512, pattern=("gla", "latent", 
                      logit_softcap=30.0)
 
 
-def lurepel_stack(width, layers, ff=None, chunk=1024, experts=16, identity=2, top=4, vocab=32768, compute_f32=False):
+def lurepel_stack(width, layers, ff=None, chunk=1024, experts=16, identity=1, top=4, vocab=32768, compute_f32=False):
     """A Lurepel-design stack at sizes that resemble a served model's layers (random-init benchmarks): heads of 128 channels,
     four query heads per key/value head, half of each head rotated, attention inside blocks of `chunk` positions; layers
     alternate a dense gated feed-forward of size ff with a mixture of `experts` experts of size ff / top (+ identity outputs)
@@ -86,8 +86,8 @@ def lurepel_stack(width, layers, ff=None, chunk=1024, experts=16, identity=2, to
     out = []
     for i in range(layers):
         l = E.LayerDesc(mixer=E.MIXER_GQA, heads=heads, kv_heads=max(1, heads // 4), dim=128, vdim=128, scale=128 ** -0.5,
-                        attn_flags=flags, mask=E.MASK_CHUNK, window=chunk, rope_dims=64, rope_pairing=1, rope_base=250000.0,
-                        rope_factor=8.0, rope_low=1.0, rope_high=4.0, rope_original=2048)
+                        attn_flags=flags, mask=E.MASK_CHUNK, window=chunk, rope_dims=64, rope_pairing=1, rope_base=500000.0,
+                        rope_factor=8.0, rope_low=1.0, rope_high=4.0, rope_original=8192)
         if i % 2 == 0:
             l.ff_kind, l.ff = E.FF_GELU_TANH, ff
         else:
