@@ -60,7 +60,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                    float scale_log2, bf16* __restrict__ out_direct, int ldo, const int* sig_wait, int sig_wait_count,
                    int* sig_done, int bank_tiles, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                    unsigned long long* trace, const int* dep_wait, int dep_count, int* dep_done,
-                   const __grid_constant__ DecodeRope rope) {
+                   const __grid_constant__ DecodeRope rope, int chunk, int sink, const float* __restrict__ head_gate, int ldg) {
   using C = DCfg<D>;
   constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -93,8 +93,12 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   const int ctx = ctx_lens[b];
   const int n_pages = (ctx + PAGE - 1) / PAGE;
   const int n_tiles_total = (ctx + BKV - 1) / BKV;
-  const int tps = (n_tiles_total + num_splits - 1) / num_splits;
-  const int t_begin = split * tps;
+  // block mask (chunk > 0): the new position sees only its own block of `chunk` positions, counted from position 0; the
+  // splits share the tiles from the one that holds the block start
+  const int kv_lo = chunk > 0 ? (ctx - 1) / chunk * chunk : 0;
+  const int t_first = kv_lo / BKV;
+  const int tps = (n_tiles_total - t_first + num_splits - 1) / num_splits;
+  const int t_begin = t_first + split * tps;
   const int t_end = min(n_tiles_total, t_begin + tps);
   float* ws_base = ws + ((size_t)(b * Hkv + kvh) * num_splits + split) * G * (D + 2);
   if (t_begin >= t_end) {
@@ -340,7 +344,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[j & 1]);
-      const bool valid = (t_begin + j) * BKV + t < ctx;
+      const bool valid = (t_begin + j) * BKV + t < ctx && (t_begin + j) * BKV + t >= kv_lo;
       float sc[G], mx[G];
 #pragma unroll
       for (int g = 0; g < G; ++g) {
@@ -422,9 +426,12 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       if (t < D) {
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-          const float lg = redl[g] + redl[kMaxG + g] + redl[2 * kMaxG + g] + redl[3 * kMaxG + g];
+          float lg = redl[g] + redl[kMaxG + g] + redl[2 * kMaxG + g] + redl[3 * kMaxG + g];
+          if (sink) lg += fast_exp2(-m_used[g]);  // one more unit in the denominator: a key of score 0 without a value
+          float gl = 1.f;
+          if (head_gate != nullptr) gl = 1.f / (1.f + __expf(-head_gate[(size_t)b * ldg + kvh * G + g]));
           out_direct[(size_t)b * ldo + (size_t)(kvh * G + g) * D + t] =
-              __float2bfloat16(lg > 0.f ? __uint_as_float(o[g]) / lg : 0.f);
+              __float2bfloat16(lg > 0.f ? __uint_as_float(o[g]) / lg * gl : 0.f);
         }
       }
     } else {
@@ -455,7 +462,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
 template <int D>
 __global__ void __launch_bounds__(D / 2)
 attn_decode_combine_kernel(const float* __restrict__ ws, bf16* __restrict__ out, int ldo, int Hq, int Hkv, int G,
-                           int num_splits) {
+                           int num_splits, int sink, const float* __restrict__ head_gate, int ldg) {
   pdl_launch_dependents();
   pdl_wait();
   const int h = blockIdx.x, b = blockIdx.y;
@@ -475,7 +482,9 @@ attn_decode_combine_kernel(const float* __restrict__ ws, bf16* __restrict__ out,
     o0 += w * p[d];
     o1 += w * p[d + 1];
   }
-  const float inv = l > 0.f ? 1.0f / l : 0.f;
+  if (sink && m != -INFINITY) l += fast_exp2(-m);
+  float inv = l > 0.f ? 1.0f / l : 0.f;
+  if (head_gate != nullptr) inv *= 1.f / (1.f + __expf(-head_gate[(size_t)b * ldg + h]));
   *reinterpret_cast<__nv_bfloat162*>(out + (size_t)b * ldo + h * D + d) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
 }
 
@@ -498,10 +507,10 @@ cudaError_t launch(cudaStream_t stream, const AttnDecodeArgs& a) {
                            a.page_table, a.max_pages, a.ctx_lens, a.workspace, a.Hkv, a.num_splits,
                            a.scale * 1.4426950408889634f, direct, a.ldo, a.sig.wait, a.sig.wait_count, a.sig.done, bank_tiles,
                            a.k_cache, a.v_cache, a.sig.trace, a.sig.dep.wait, a.sig.dep.wait_count, a.sig.dep.done,
-                           a.num_splits == 1 ? a.rope : DecodeRope{});
+                           a.num_splits == 1 ? a.rope : DecodeRope{}, a.block_mask, a.unit_sink, a.head_gate, a.ldg);
   if (e != cudaSuccess || direct) return e;
   return launch_k(attn_decode_combine_kernel<D>, dim3(a.Hq, a.B), dim3(D / 2), 0, stream, true,
-                  (const float*)a.workspace, a.out, a.ldo, a.Hq, a.Hkv, G, a.num_splits);
+                  (const float*)a.workspace, a.out, a.ldo, a.Hq, a.Hkv, G, a.num_splits, a.unit_sink, a.head_gate, a.ldg);
 }
 
 }  // namespace
@@ -528,7 +537,7 @@ size_t attn_decode_workspace_floats(int B, int Hq, int D, int num_splits) {
 
 cudaError_t attn_decode(cudaStream_t stream, const AttnDecodeArgs& a) {
   if (a.B <= 0) return cudaSuccess;
-  if (a.page_size != PAGE || a.Hq % a.Hkv || a.num_splits < 1 || a.num_pages <= 0) return cudaErrorInvalidValue;
+  if (a.page_size != PAGE || a.Hq % a.Hkv || a.num_splits < 1 || a.num_pages <= 0 || a.block_mask < 0) return cudaErrorInvalidValue;
   const int G = a.Hq / a.Hkv;
   if (a.D == 128) {
     switch (G) {

@@ -201,6 +201,7 @@ class Engine {
     float *moe_z = nullptr, *moe_w = nullptr, *moe_y = nullptr;
     int32_t* moe_ids = nullptr;
     int ldz = 0;
+    float* dec_ws = nullptr;  // split partials of the tensor-core decode attention (grouped-query layers, bf16 mode)
     bf16* att16 = nullptr;  // grouped-query layers, bf16 mode: output of the fused tcgen05 attention [T][heads * vdim]
     int ldatt = 0;
     // experts as grouped tensor-core products (bf16 mode): items sorted by expert into a row buffer of moe_rows rows

@@ -180,6 +180,7 @@ struct StackDims {
   int n1 = 0, n2 = 0, q = 0, qa = 0, cx = 0, mo = 0;
   int moe_r = 0, moe_top = 0, rope_half = 0;
   int gu = 0;                // widest [gate | up] row of a plain gated unit (bf16 intermediate of the tensor-core path)
+  int att_heads = 0, att_dim = 0;  // ... and their most heads / widest head (split workspace of the decode kernel)
   int att = 0;               // grouped-query layers the fused tcgen05 attention takes: widest heads * vdim
   int moe_e = 0, moe_f = 0;  // grouped tensor-core experts: most experts / widest expert over the layers that qualify
 };
@@ -209,7 +210,11 @@ static StackDims stack_dims(const Model& m, int max_ctx) {
     } else if (l.mixer == HB_MIXER_GQA) {
       d.n2 = std::max(d.n2, l.heads * l.dim);
       d.rope_half += l.rope_dims / 2;
-      if (gqa_fused_ok(m, l, max_ctx)) d.att = std::max(d.att, l.heads * l.vdim);
+      if (gqa_fused_ok(m, l, max_ctx)) {
+        d.att = std::max(d.att, l.heads * l.vdim);
+        d.att_heads = std::max(d.att_heads, l.heads);
+        d.att_dim = std::max(d.att_dim, l.dim);
+      }
     } else {
       d.n2 = std::max(d.n2, l.heads * (l.dim + l.rot_dim));
       d.q = std::max(d.q, l.q_rank);
@@ -236,7 +241,7 @@ size_t Engine::workspace_bytes_stack() const {
   const int n1 = dm.n1, n2 = dm.n2, q = dm.q, qa = dm.qa, cx = dm.cx, mo = dm.mo;
   size_t b = 0;
   b += al256((size_t)std::max(dm.rope_half, 1) * 8) + al256(T * 2 * (size_t)std::max(dm.rope_half, 1) * 4);
-  if (dm.att > 0) b += al256(T * (size_t)up8(dm.att) * 2);
+  if (dm.att > 0) b += al256(T * (size_t)up8(dm.att) * 2) + al256(attn_decode_workspace_floats(cfg_.max_seqs, dm.att_heads, dm.att_dim, 16) * 4);
   if (dm.moe_r > 0) {
     const size_t rows = dm.moe_e > 0 ? (size_t)moe_group_max_rows((int)T * dm.moe_top, dm.moe_e) : T * (size_t)dm.moe_top;
     b += al256(T * (size_t)std::max(64, up8(dm.moe_r)) * 4) + 2 * al256(T * (size_t)dm.moe_top * 4) + al256(rows * W * 4);
@@ -327,6 +332,7 @@ int Engine::alloc_runtime_stack() {
   if (dm.att > 0) {
     sk_.ldatt = up8(dm.att);
     sk_.att16 = (bf16*)take(T * (size_t)sk_.ldatt * 2);
+    sk_.dec_ws = (float*)take(attn_decode_workspace_floats(cfg_.max_seqs, dm.att_heads, dm.att_dim, 16) * 4);
   }
   if (dm.moe_r > 0) {
     sk_.ldz = std::max(64, up8(dm.moe_r));
@@ -544,15 +550,38 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       bool fused = gqa_fused_ok(model_, l, cfg_.max_ctx) && k.att16 && k.q16 && (H * Dk) % 8 == 0 && page_ == 64;
       int longest = 0;
       for (const StepEntry& en : step_entries_) longest = std::max(longest, en.n);
+      // steps of single tokens: the Llama path's tensor-core decode kernel (keys and values streamed once per kv head by TMA)
+      // with the block start, the unit of the denominator and the gate as parameters
+      const int rep = H / G;
+      static const bool dec_off = [] { const char* e = getenv("HB_STACK_TC_DECODE"); return e && atoi(e) == 0; }();
+      const bool tc_dec = fused && !dec_off && longest == 1 && T == B && B <= cfg_.max_seqs && k.dec_ws && stack_tc(W, H * Dv, H * Dv, W) &&
+                          (rep == 1 || rep == 2 || rep == 3 || rep == 4 || rep == 6 || rep == 8);
       fused = fused && longest >= kAttDenseMin;
-      pa.q = fused ? nullptr : k.p2; pa.ldq = H * Dk; pa.q_b16 = fused ? k.q16 : nullptr;
+      pa.q = (fused || tc_dec) ? nullptr : k.p2; pa.ldq = H * Dk; pa.q_b16 = (fused || tc_dec) ? k.q16 : nullptr;
       pa.k_cache = kplane; pa.v_cache = vplane; pa.f32 = f32;
       pa.slots = slots; pa.positions = positions;
       pa.cs = k.layer_set[i] >= 0 ? k.rope_cs[k.layer_set[i]] : nullptr; pa.rope_dims = l.rope_dims; pa.pairing = l.rope_pairing;
       pa.H = H; pa.G = G; pa.D = Dk; pa.Dv = Dv; pa.page_size = page_;
       pa.unit_norm = (l.attn_flags & HB_ATTN_QK_UNIT_NORM) != 0; pa.eps = sd.norm_eps; pa.T = T;
       SPAN(3, 8.0 * T * (H + 2 * G) * Dk, gqa_prep(stream_, pa));
-      if (fused) {
+      if (tc_dec) {
+        AttnDecodeArgs da{};
+        da.q = k.q16; da.ldq = H * Dk;
+        da.k_cache = (const bf16*)kplane; da.v_cache = (const bf16*)vplane;
+        da.page_table = pt; da.max_pages = max_pages_per_seq_;
+        da.ctx_lens = (const int32_t*)(d_step_ + L.ctx);
+        da.out = mo16; da.ldo = H * Dv;
+        da.workspace = k.dec_ws;
+        da.B = B; da.Hq = H; da.Hkv = G; da.D = Dk; da.page_size = page_;
+        const int want = (int)(0.8 * 2 * (cfg_.sm_budget > 0 ? cfg_.sm_budget : 148));
+        da.num_splits = std::max(1, std::min(16, (want + B * G - 1) / (B * G)));
+        da.scale = l.scale; da.num_pages = num_pages_;
+        da.block_mask = l.mask == HB_MASK_CHUNK ? l.window : 0;
+        da.unit_sink = (l.attn_flags & HB_ATTN_UNIT_SINK) ? 1 : 0;
+        if (l.attn_flags & HB_ATTN_HEAD_GATE) { da.head_gate = k.p1 + w.off_g; da.ldg = ldin; }
+        SPAN(2, 2.0 * B * G * (double)std::min(l.window, cfg_.max_ctx) * (Dk + Dv), attn_decode(stream_, da));
+        if (da.num_splits > 1) launches_.fetch_add(1, std::memory_order_relaxed);  // combine kernel
+      } else if (fused) {
         AttnPrefillArgs fa{};
         fa.q = k.q16; fa.ldq = H * Dk;
         fa.k = nullptr; fa.ldk = 0; fa.v = nullptr; fa.ldv = 0;

@@ -183,6 +183,10 @@ struct AttnDecodeArgs {
   int num_pages;                   // pages in the pool (TMA tensor-map extent)
   StreamSig sig;                   // HBM hand-over with the neighbouring streaming kernels (optional)
   DecodeRope rope;                 // build q / K / V from the QKV GEMM's slabs inside the kernel (num_splits == 1 only)
+  // block_mask > 0: the token sees only the keys of its own block of block_mask positions (blocks counted from position 0);
+  // unit_sink: one unit added to the softmax denominator; head_gate: optional [B][>= Hq] fp32, head h leaves times its sigmoid
+  int block_mask = 0, unit_sink = 0;
+  const float* head_gate = nullptr; int ldg = 0;
 };
 cudaError_t attn_decode(cudaStream_t stream, const AttnDecodeArgs& a);
 size_t attn_decode_workspace_floats(int B, int Hq, int D, int num_splits);
