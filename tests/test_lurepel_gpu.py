@@ -225,6 +225,33 @@ def test_far_keys_and_page_borders():
             assert row_err(replay(e, toks, [255, 2, 1, 1, 1, 2]), want).max() < TOL[f32]  # decoding over the page border at 256
 
 
+@pytest.mark.parametrize("shape", [dict(dim=64, heads=6, kv_heads=2, chunk=70), dict(dim=128, heads=8, kv_heads=1, chunk=150),
+                                   dict(dim=64, heads=2, kv_heads=2, chunk=0)])
+def test_single_token_steps_on_the_tensor_core_decode_kernel(shape):
+    # serving mode, head sizes of the TMA decode kernel: block starts inside its 128-key tiles, blocks that end while decoding,
+    # one to three sequences per step at different depths (one split per CTA up to sixteen)
+    cfg = ref.random_config(width=128, vocab=256, rot_dims=32, order=("dense", None), **shape)
+    sd = ref.random_state_dict(cfg, seed=59)
+    o = ref.LurepelOracle(cfg, sd)
+    seqs = [tokens(70 + i, n, cfg["vocab"]) for i, n in enumerate((330, 200, 150))]
+    want = [o.forward(s) for s in seqs]
+    with make_engine(cfg, sd, 0, ctx=384) as e:
+        assert row_err(replay(e, seqs[0], [5]), want[0]).max() < TOL[0]  # 325 single-token steps of one sequence
+        ids = [e.seq_open() for _ in seqs]
+        starts = (130, 3, 64)
+        for i, sid in enumerate(ids):
+            e.seq_step([(sid, seqs[i][:starts[i]], [])])
+        got, at = [[] for _ in seqs], list(starts)
+        while any(at[i] < len(seqs[i]) for i in range(3)):
+            live = [i for i in range(3) if at[i] < len(seqs[i])]
+            out = e.seq_step([(ids[i], [seqs[i][at[i]]], [0]) for i in live])
+            for r, i in enumerate(live):
+                got[i].append(out[r])
+                at[i] += 1
+        for i in range(3):
+            assert row_err(np.stack(got[i]), want[i][starts[i]:]).max() < TOL[0]
+
+
 def test_long_decoding_over_blocks_and_pages():
     cfg = ref.random_config(chunk=50)
     sd = ref.random_state_dict(cfg, seed=23)
