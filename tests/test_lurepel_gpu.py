@@ -92,6 +92,7 @@ CONFIGS = {
     "top_one_no_identity": dict(order=("moe", "moe"), identity=0, top=1, experts=3),
     "every_output_chosen": dict(order=("moe",), identity=1, top=4, experts=3),
     "one_expert_many_identities": dict(order=("moe",), identity=3, top=2, experts=1),
+    "many_experts": dict(order=("moe", "dense"), experts=70, identity=2, top=5, expert_ff=24),  # router wider than one MMA tile
     "layers_differ": dict(order=("moe", "dense", "moe"), per_layer={0: dict(heads=2, kv_heads=1, dim=40, mask=dict(size=7)),
                                                                     2: dict(heads=8, kv_heads=4, dim=8, rot=dict(base=30.0, dims=4))}),
     # head sizes of the fused tensor-core attention with blocks shorter than its 64-key tiles / longer than a page
