@@ -207,7 +207,8 @@ class Engine {
     // experts as grouped tensor-core products (bf16 mode): items sorted by expert into a row buffer of moe_rows rows
     int moe_rows = 0;
     int32_t *moe_row_of = nullptr, *moe_src = nullptr, *moe_tiles = nullptr;
-    bf16 *moe_a16 = nullptr, *moe_h16 = nullptr;
+    bf16 *moe_a16 = nullptr, *moe_h16 = nullptr, *moe_y16 = nullptr;
+    int32_t* moe_scratch = nullptr;
     bf16* gu16 = nullptr;  // [gate | up] products of a gated unit as bf16 (tensor-core path of steps of > 256 tokens, experts)
     // rotation of grouped-query layers: distinct frequency sets (device, fp64; layers with equal rotation share one), the
     // step's cos / sin table of every set, and each layer's set (-1: none)

@@ -244,9 +244,10 @@ size_t Engine::workspace_bytes_stack() const {
   if (dm.att > 0) b += al256(T * (size_t)up8(dm.att) * 2) + al256(attn_decode_workspace_floats(cfg_.max_seqs, dm.att_heads, dm.att_dim, 16) * 4);
   if (dm.moe_r > 0) {
     const size_t rows = dm.moe_e > 0 ? (size_t)moe_group_max_rows((int)T * dm.moe_top, dm.moe_e) : T * (size_t)dm.moe_top;
-    b += al256(T * (size_t)std::max(64, up8(dm.moe_r)) * 4) + 2 * al256(T * (size_t)dm.moe_top * 4) + al256(rows * W * 4);
+    b += al256(T * (size_t)std::max(64, up8(dm.moe_r)) * 4) + 2 * al256(T * (size_t)dm.moe_top * 4) + al256(T * (size_t)dm.moe_top * W * 4);
     if (dm.moe_e > 0)
-      b += al256(T * (size_t)dm.moe_top * 4) + al256(rows * 4) + al256(rows / 128 * 4) + al256(rows * W * 2) + al256(rows * dm.moe_f * 2);
+      b += al256(T * (size_t)dm.moe_top * 4) + al256(rows * 4) + al256(rows / 128 * 4) + 2 * al256(rows * W * 2) + al256(rows * dm.moe_f * 2) +
+           al256((size_t)3 * dm.moe_e * 4);
   }
   if (!sd.compute_f32) {
     const size_t rows = dm.moe_e > 0 ? (size_t)moe_group_max_rows((int)T * dm.moe_top, dm.moe_e) : 0;
@@ -340,7 +341,7 @@ int Engine::alloc_runtime_stack() {
     sk_.moe_ids = (int32_t*)take(T * (size_t)dm.moe_top * 4);
     sk_.moe_w = (float*)take(T * (size_t)dm.moe_top * 4);
     const size_t rows = dm.moe_e > 0 ? (size_t)moe_group_max_rows((int)T * dm.moe_top, dm.moe_e) : T * (size_t)dm.moe_top;
-    sk_.moe_y = (float*)take(rows * W * 4);
+    sk_.moe_y = (float*)take(T * (size_t)dm.moe_top * W * 4);  // per-item outputs of the GEMV path
     if (dm.moe_e > 0) {
       sk_.moe_rows = (int)rows;
       sk_.moe_row_of = (int32_t*)take(T * (size_t)dm.moe_top * 4);
@@ -348,6 +349,8 @@ int Engine::alloc_runtime_stack() {
       sk_.moe_tiles = (int32_t*)take(rows / 128 * 4);
       sk_.moe_a16 = (bf16*)take(rows * W * 2);
       sk_.moe_h16 = (bf16*)take(rows * dm.moe_f * 2);
+      sk_.moe_y16 = (bf16*)take(rows * W * 2);
+      sk_.moe_scratch = (int32_t*)take((size_t)3 * dm.moe_e * 4);
     }
   }
   if (!sd.compute_f32) {
@@ -728,7 +731,8 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       if (moe_grouped_ok(model_, l) && k.moe_a16 && items >= 2 * E) {
         // items sorted by expert into 128-row segments; both products of every expert in two grouped tcgen05 launches
         const int rows = moe_group_max_rows(items, E);
-        SPAN(3, 12.0 * items, moe_group_rows(stream_, k.moe_ids, items, l.top_k, E, k.moe_row_of, k.moe_src, k.moe_tiles));
+        SPAN(3, 12.0 * items, moe_group_rows(stream_, k.moe_ids, items, l.top_k, E, k.moe_row_of, k.moe_src, k.moe_tiles, k.moe_scratch));
+        if (items > 4096) launches_.fetch_add(2, std::memory_order_relaxed);  // three kernels behind one call
         SPAN(3, 4.0 * rows * W, moe_gather_rows(stream_, x16, W, k.moe_src, k.moe_a16, rows));
         if (w.gu_packed) {  // silu(gate) * up on the accumulators' way out
           GemmArgs g1{k.moe_a16, W, (const bf16*)w.w_gu, W, k.moe_h16, F, nullptr, 0, nullptr, rows, 2 * F, W, EPI_SWIGLU, 0};
@@ -740,10 +744,10 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
           SPAN(0, 4.0 * rows * F * W, gemm_bf16_tn(stream_, g1));
           SPAN(3, 6.0 * rows * F, gated_unit_b16(stream_, k.gu16, 2 * F, GLU_SILU, k.moe_h16, rows, F));
         }
-        GemmArgs g2{k.moe_h16, F, (const bf16*)w.w_down, F, k.moe_y, W, nullptr, 0, nullptr, rows, W, F, EPI_F32, 0};
+        GemmArgs g2{k.moe_h16, F, (const bf16*)w.w_down, F, k.moe_y16, W, nullptr, 0, nullptr, rows, W, F, EPI_NONE, 0};
         g2.m_tile_group = k.moe_tiles; g2.groups = E;
         SPAN(0, 2.0 * rows * F * W, gemm_bf16_tn(stream_, g2));
-        SPAN(3, 4.0 * T * (l.top_k + 2) * W, moe_combine_rows(stream_, k.x, k.moe_y, k.moe_row_of, k.moe_w, l.top_k, k.y, T, W));
+        SPAN(3, 2.0 * T * (l.top_k + 4) * W, moe_combine_rows(stream_, k.x, k.moe_y16, k.moe_row_of, k.moe_w, l.top_k, k.y, T, W));
       } else {
         SPAN(5, 6.0 * items * F * W, moe_expert_rows(stream_, k.x, x16, w.w_gu, w.w_down, f32, k.moe_ids, l.top_k, E, F, W, k.moe_y, T, w.gu_packed));
         SPAN(3, 4.0 * T * (l.top_k + 2) * W, moe_combine(stream_, k.x, k.moe_y, k.moe_ids, k.moe_w, l.top_k, E, k.y, T, W));

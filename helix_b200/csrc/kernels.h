@@ -428,12 +428,12 @@ cudaError_t moe_expert_rows(cudaStream_t s, const float* x, const bf16* x_b16, c
 // a row buffer of moe_group_max_rows(items, E) rows whose per-expert segments start on multiples of 128 rows (row_of[item] =
 // its row or -1 for an identity output, src_of_row[row] = its token or -1, tile_group[row / 128] = the expert whose weights
 // multiply that m tile — GemmArgs::m_tile_group); moe_gather_rows copies the tokens' bf16 rows into it (zeros elsewhere);
-// moe_combine_rows is moe_combine over the row buffer.
+// moe_combine_rows is moe_combine over the row buffer (the experts' outputs as bf16, the sum in fp32).
 int moe_group_max_rows(int n_items, int E);
 cudaError_t moe_group_rows(cudaStream_t s, const int32_t* ids, int n_items, int top_k, int E, int32_t* row_of, int32_t* src_of_row,
-                           int32_t* tile_group);
+                           int32_t* tile_group, int32_t* scratch);  // scratch: 3 E ints
 cudaError_t moe_gather_rows(cudaStream_t s, const bf16* x16, int W, const int32_t* src_of_row, bf16* a16, int rows);
-cudaError_t moe_combine_rows(cudaStream_t s, const float* x, const float* y, const int32_t* row_of, const float* wts, int top_k,
+cudaError_t moe_combine_rows(cudaStream_t s, const float* x, const bf16* y, const int32_t* row_of, const float* wts, int top_k,
                              float* out, int T, int W);
 // out[t, :] = sum_k wts[t, k] * (ids[t, k] < E ? y[(t, k), :] : x[t, :]), k in order
 cudaError_t moe_combine(cudaStream_t s, const float* x, const float* y, const int32_t* ids, const float* wts, int top_k, int E,

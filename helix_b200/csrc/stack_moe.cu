@@ -273,12 +273,56 @@ __global__ void moe_combine_kernel(const float* __restrict__ x, const float* __r
   }
 }
 
-// Groups the (token, choice) items by expert for the grouped tensor-core products.  One block.  Expert e's items get the rows
+// Groups the (token, choice) items by expert for the grouped tensor-core products, in three small launches: count per
+// expert (and mark every row of the buffer empty), offsets and the m tiles' experts, rows.  Expert e's items get the rows
 // [off_e, off_e + count_e) of a row buffer whose per-expert segments start on multiples of 128 rows (one m tile never mixes
 // experts); rows between segments and behind the last one stay empty (src -1) and belong to expert 0's tiles, so every tile
 // of the buffer can be multiplied without the host knowing the counts.  Which row of its segment an item gets depends on
-// arrival order; a row's product does not depend on where the row sits.
-__global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t* __restrict__ ids, int n_items, int top_k, int E, int max_rows,
+// arrival order; a row's product does not depend on where the row sits.  scratch: [E] counts | [E] offsets | [E] cursors.
+__global__ void moe_count_kernel(const int32_t* __restrict__ ids, int n_items, int E, int max_rows, int32_t* __restrict__ src_of_row,
+                                 int32_t* __restrict__ scratch) {
+  const int stride = gridDim.x * blockDim.x;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < max_rows; i += stride) {
+    src_of_row[i] = -1;
+    if (i < n_items) {
+      const int e = ids[i];
+      if (e < E) atomicAdd(&scratch[e], 1);
+    }
+  }
+}
+__global__ void moe_offsets_kernel(int E, int max_rows, int32_t* __restrict__ scratch, int32_t* __restrict__ tile_group) {
+  __shared__ int s_off[4097];
+  if (threadIdx.x == 0) {
+    int o = 0;
+    for (int e = 0; e < E; ++e) {
+      s_off[e] = o;
+      o += (scratch[e] + 127) / 128 * 128;
+    }
+    s_off[E] = o;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    scratch[E + e] = s_off[e];
+    scratch[2 * E + e] = 0;
+    for (int tl = s_off[e] / 128; tl < s_off[e + 1] / 128; ++tl) tile_group[tl] = e;
+  }
+  for (int tl = s_off[E] / 128 + threadIdx.x; tl < max_rows / 128; tl += blockDim.x) tile_group[tl] = 0;
+}
+__global__ void moe_rows_kernel(const int32_t* __restrict__ ids, int n_items, int top_k, int E, int32_t* __restrict__ scratch,
+                                int32_t* __restrict__ row_of, int32_t* __restrict__ src_of_row) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_items) return;
+  const int e = ids[i];
+  int r = -1;
+  if (e < E) {
+    r = scratch[E + e] + atomicAdd(&scratch[2 * E + e], 1);
+    src_of_row[r] = i / top_k;
+  }
+  row_of[i] = r;
+}
+
+// The same grouping by one block (steps of few items: one launch instead of three).
+__global__ void __launch_bounds__(1024) moe_group_small_kernel(const int32_t* __restrict__ ids, int n_items, int top_k, int E, int max_rows,
                                                          int32_t* __restrict__ row_of, int32_t* __restrict__ src_of_row,
                                                          int32_t* __restrict__ tile_group) {
   extern __shared__ int smi[];
@@ -326,7 +370,7 @@ __global__ void __launch_bounds__(128) moe_gather_kernel(const bf16* __restrict_
   for (int i = threadIdx.x; i < W / 8; i += blockDim.x) dst[i] = src < 0 ? make_uint4(0, 0, 0, 0) : from[i];
 }
 
-__global__ void moe_combine_rows_kernel(const float* __restrict__ x, const float* __restrict__ y, const int32_t* __restrict__ row_of,
+__global__ void moe_combine_rows_kernel(const float* __restrict__ x, const bf16* __restrict__ y, const int32_t* __restrict__ row_of,
                                         const float* __restrict__ wts, int top_k, float* __restrict__ out, int W) {
   const int t = blockIdx.x;
   for (int c = threadIdx.x; c < W; c += blockDim.x) {
@@ -334,7 +378,7 @@ __global__ void moe_combine_rows_kernel(const float* __restrict__ x, const float
     for (int k = 0; k < top_k; ++k) {
       const size_t item = (size_t)t * top_k + k;
       const int r = row_of[item];
-      const float v = r >= 0 ? y[(size_t)r * W + c] : x[(size_t)t * W + c];
+      const float v = r >= 0 ? __bfloat162float(y[(size_t)r * W + c]) : x[(size_t)t * W + c];
       acc = fmaf(wts[item], v, acc);
     }
     out[(size_t)t * W + c] = acc;
@@ -346,10 +390,19 @@ __global__ void moe_combine_rows_kernel(const float* __restrict__ x, const float
 int moe_group_max_rows(int n_items, int E) { return (n_items + 127) / 128 * 128 + E * 128; }
 
 cudaError_t moe_group_rows(cudaStream_t s, const int32_t* ids, int n_items, int top_k, int E, int32_t* row_of, int32_t* src_of_row,
-                           int32_t* tile_group) {
+                           int32_t* tile_group, int32_t* scratch) {
   if (n_items <= 0) return cudaSuccess;
   if (E > 4096) return cudaErrorInvalidValue;
-  moe_group_kernel<<<1, 1024, (size_t)3 * E * 4, s>>>(ids, n_items, top_k, E, moe_group_max_rows(n_items, E), row_of, src_of_row, tile_group);
+  const int max_rows = moe_group_max_rows(n_items, E);
+  if (n_items <= 4096) {
+    moe_group_small_kernel<<<1, 1024, (size_t)3 * E * 4, s>>>(ids, n_items, top_k, E, max_rows, row_of, src_of_row, tile_group);
+    return cudaGetLastError();
+  }
+  cudaError_t e = cudaMemsetAsync(scratch, 0, (size_t)E * 4, s);
+  if (e != cudaSuccess) return e;
+  moe_count_kernel<<<std::min((max_rows + 255) / 256, 1184), 256, 0, s>>>(ids, n_items, E, max_rows, src_of_row, scratch);
+  moe_offsets_kernel<<<1, 256, 0, s>>>(E, max_rows, scratch, tile_group);
+  moe_rows_kernel<<<(n_items + 255) / 256, 256, 0, s>>>(ids, n_items, top_k, E, scratch, row_of, src_of_row);
   return cudaGetLastError();
 }
 
@@ -360,7 +413,7 @@ cudaError_t moe_gather_rows(cudaStream_t s, const bf16* x16, int W, const int32_
   return cudaGetLastError();
 }
 
-cudaError_t moe_combine_rows(cudaStream_t s, const float* x, const float* y, const int32_t* row_of, const float* wts, int top_k,
+cudaError_t moe_combine_rows(cudaStream_t s, const float* x, const bf16* y, const int32_t* row_of, const float* wts, int top_k,
                              float* out, int T, int W) {
   if (T <= 0) return cudaSuccess;
   moe_combine_rows_kernel<<<T, 256, 0, s>>>(x, y, row_of, wts, top_k, out, W);
