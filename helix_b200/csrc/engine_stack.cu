@@ -1,4 +1,4 @@
-// Layer-list decoders (HB_ARCH_RISEPEL) inside hb::Engine: model load, the latent page pool and recurrent state slots,
+// Layer-list decoders (HB_ARCH_STACK: the Risepel and Lurepel designs) inside hb::Engine: model load, the page pool's planes and recurrent state slots,
 // the step's forward pass and the driven-sequence entry points.  Scheduling, page bookkeeping, the step block, sampling
 // and request records are the engine's own (engine.cu); this file adds what differs from the Llama path:
 //   * the residual stream is fp32 and post-normed; every sublayer reads the stream itself;
@@ -8,6 +8,14 @@
 //   * attention layers cache one latent row per token ([c | k_rot]); a layer may read the rows of an earlier layer;
 //   * recurrent layers keep one fp32 matrix per head in a state slot; an entry that starts at position 0 starts from zero,
 //     so a slot needs no clearing when it changes hands.
+//   * grouped-query layers keep two planes of the pool (rotated unit-norm keys, raw values) in the Llama path's
+//     [page][kv_head][64][D] layout, so prompt portions and single-token steps run on that path's fused tcgen05 attention
+//     kernels (block mask, unit sink and head gate are parameters of both); other shapes, short portions and the exact
+//     mode take the per-token kernel;
+//   * the residual step norms the sum (x <- norm(alpha x + f(x))) or the sublayer's output (x <- x + norm(f(x)));
+//   * feed-forwards: clamped gated unit, tanh-GELU gated unit (gated epilogue of the GEMM), mixture of experts (router and
+//     choice in fp32, items sorted by expert into 128-row segments on the device, two grouped tcgen05 products; nothing
+//     returns to the host, so decode graphs stay static).
 #include "engine.h"
 #include "launch.h"
 
